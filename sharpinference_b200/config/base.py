@@ -155,8 +155,13 @@ def read_config_json(model_dir: str) -> dict:
 
 
 def architecture_name(obj: dict, where: str = "config.json") -> str:
-    """The name under which the model class is registered: ``architectures[0]``."""
+    """The name under which the model class is registered: ``architectures[0]``, or the string under
+    ``architecture`` in files that name one model class only."""
     archs = obj.get("architectures")
     if isinstance(archs, Sequence) and not isinstance(archs, str) and len(archs) >= 1 and isinstance(archs[0], str):
         return archs[0]
-    raise ConfigError(f"{where}: key 'architectures' must be a non-empty list of names, found {archs!r}")
+    single = obj.get("architecture")
+    if archs is None and isinstance(single, str) and single:
+        return single
+    raise ConfigError(f"{where}: key 'architectures' must be a non-empty list of names (or 'architecture' one "
+                      f"name), found {archs!r}")

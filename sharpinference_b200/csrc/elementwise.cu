@@ -325,6 +325,74 @@ SHARPI_API int sharpi_add_bias(float* y, const float* bias, int M, int N, cudaSt
     return SHARPI_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// out[m, n] = act(y[m, n] + bias[n]): the activation of a feed-forward whose first product came back in fp32.
+//   ACT_RELU2      max(z, 0)^2
+//   ACT_GELU_TANH  0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+//   ACT_SILU       z / (1 + exp(-z))
+// ---------------------------------------------------------------------------------------
+enum SharpiAct : int { ACT_RELU2 = 0, ACT_GELU_TANH = 1, ACT_SILU = 2 };
+
+template <int ACT> __device__ __forceinline__ float activate(float z) {
+    if (ACT == ACT_RELU2) { const float r = fmaxf(z, 0.0f); return r * r; }
+    if (ACT == ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
+
+template <typename TO, int ACT>
+__global__ void bias_act_kernel(const float* __restrict__ y, const float* __restrict__ bias, TO* __restrict__ out,
+                                int N) {
+    pdl_wait();
+    const size_t m = blockIdx.x;
+    for (int n = blockIdx.y * blockDim.x + threadIdx.x; n < N; n += gridDim.y * blockDim.x) {
+        const float z = y[m * N + n] + (bias ? bias[n] : 0.0f);
+        out[m * N + n] = from_float<TO>(activate<ACT>(z));
+    }
+}
+
+template <typename TO>
+static int launch_bias_act(const float* y, const float* bias, TO* out, int M, int N, int act, cudaStream_t stream) {
+    int by = (N + 255) / 256;
+    if (by > 64) by = 64;
+    const dim3 grid(M, by);
+    if (act == ACT_RELU2) SHARPI_LAUNCH_PDL((bias_act_kernel<TO, ACT_RELU2>), grid, 256, 0, stream, y, bias, out, N);
+    else if (act == ACT_GELU_TANH) SHARPI_LAUNCH_PDL((bias_act_kernel<TO, ACT_GELU_TANH>), grid, 256, 0, stream, y, bias, out, N);
+    else if (act == ACT_SILU) SHARPI_LAUNCH_PDL((bias_act_kernel<TO, ACT_SILU>), grid, 256, 0, stream, y, bias, out, N);
+    else return SHARPI_BAD_ARGUMENT;
+    return SHARPI_OK;
+}
+
+SHARPI_API int sharpi_bias_act(const float* y, const float* bias, void* out, int out_dtype, int M, int N, int act,
+                               cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return SHARPI_OK;
+    if (out_dtype == SHARPI_F32) return launch_bias_act<float>(y, bias, (float*)out, M, N, act, stream);
+    if (out_dtype == SHARPI_BF16) return launch_bias_act<bf16>(y, bias, (bf16*)out, M, N, act, stream);
+    return SHARPI_BAD_ARGUMENT;
+}
+
+// out[t, 0:H] = a[t] + delta[t] (delta nullable), out[t, H:2H] = b[t]: two streams side by side as the input of
+// one product, in the dtype of that product's operand.
+template <typename TO>
+__global__ void concat2_kernel(const float* __restrict__ a, const float* __restrict__ delta,
+                               const float* __restrict__ b, TO* __restrict__ out, int H) {
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = a[t * H + i] + (delta ? delta[t * H + i] : 0.0f);
+        out[t * 2 * H + i] = from_float<TO>(v);
+        out[t * 2 * H + H + i] = from_float<TO>(b[t * H + i]);
+    }
+}
+
+SHARPI_API int sharpi_concat2(const float* a, const float* delta, const float* b, void* out, int out_dtype, int T,
+                              int H, cudaStream_t stream) {
+    if (T <= 0 || H <= 0) return SHARPI_OK;
+    if (out_dtype == SHARPI_F32) SHARPI_LAUNCH_PDL(concat2_kernel<float>, T, 256, 0, stream, a, delta, b, (float*)out, H);
+    else if (out_dtype == SHARPI_BF16) SHARPI_LAUNCH_PDL(concat2_kernel<bf16>, T, 256, 0, stream, a, delta, b, (bf16*)out, H);
+    else return SHARPI_BAD_ARGUMENT;
+    return SHARPI_OK;
+}
+
 // The GPU's nanosecond clock into slot[index]: a marker between the launches of a stream, for timelines of a
 // step taken inside a captured graph, where host-side timing sees nothing.
 __global__ void timestamp_kernel(unsigned long long* slots, int index) {

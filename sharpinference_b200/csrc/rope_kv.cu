@@ -34,6 +34,8 @@ struct QkvPostArgs {
     int max_blocks, page_size;
     int pairing;
     float l2_eps;            // < 0: no norm
+    int l2_count;            // the mean of squares divides by this many elements (d, or fewer when the head
+                             // is padded with zeros beyond its own size)
     float temp_attn_scale;   // temperature factor on q; floor_scale <= 0: none
     float temp_floor_scale;
     int write_kv;            // 0: this layer reads a cache that another layer writes
@@ -106,7 +108,7 @@ __global__ void qkv_post_kernel(QkvPostArgs a) {
     float scale = 1.0f;
     if (a.l2_eps >= 0.0f) {
         ss = warp_sum(ss);
-        scale = 1.0f / sqrtf(ss / (float)d + a.l2_eps);
+        scale = 1.0f / sqrtf(ss / (float)a.l2_count + a.l2_eps);
     }
     if (is_q && a.temp_floor_scale > 0.0f) {
         const float steps = floorf(((float)pos + 1.0f) / a.temp_floor_scale);
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
             }
             if (a.l2_eps >= 0.0f) {
                 ss = warp_sum(ss);
-                scale = 1.0f / sqrtf(ss / (float)d + a.l2_eps);
+                scale = 1.0f / sqrtf(ss / (float)a.l2_count + a.l2_eps);
             }
             if (is_q) scale *= temp;
         }
@@ -240,7 +242,7 @@ __global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
 SHARPI_API int sharpi_qkv_post(const float* qkv, const int* positions, const int* row_req, const int* block_table,
                                const float* inv_freq, void* q_out, void* kv_base, int out_dtype, int T, int nq,
                                int nkv, int d, int max_blocks, int page_size, int pairing, float l2_eps,
-                               float temp_attn_scale, float temp_floor_scale, int write_kv,
+                               float temp_attn_scale, float temp_floor_scale, int write_kv, int l2_count,
                                cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (nq <= 0 || nkv <= 0 || d <= 0 || (d & 1) || d > 512 || page_size <= 0 || max_blocks <= 0)
@@ -251,6 +253,7 @@ SHARPI_API int sharpi_qkv_post(const float* qkv, const int* positions, const int
     a.inv_freq = inv_freq; a.q_out = q_out; a.kv_base = kv_base;
     a.T = T; a.nq = nq; a.nkv = nkv; a.d = d; a.max_blocks = max_blocks; a.page_size = page_size;
     a.pairing = inv_freq ? pairing : ROPE_NONE; a.l2_eps = l2_eps;
+    a.l2_count = (l2_count > 0 && l2_count <= d) ? l2_count : d;
     a.temp_attn_scale = temp_attn_scale; a.temp_floor_scale = temp_floor_scale; a.write_kv = write_kv;
     if (out_dtype != SHARPI_F32 && out_dtype != SHARPI_BF16) return SHARPI_BAD_ARGUMENT;
     const long long work = (long long)T * (nq + 2 * nkv);

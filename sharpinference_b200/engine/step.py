@@ -86,6 +86,9 @@ class StepRunner:
         # run eagerly, never as a replayed graph.
         self.trace_layers = False
         self.last_layer_norms: list = []
+        # `trace_streams`: the whole residual stream [T, H] after every scheduled block, in `last_layer_streams`
+        self.trace_streams = False
+        self.last_layer_streams: list = []
         # after every step, read the word in which a tensor-core kernel records a wait that gave up
         # (a 4-byte copy; the step's result is read by the host right after anyway)
         self.check_kernel_status = True
@@ -96,8 +99,11 @@ class StepRunner:
         # step's metadata lives in one static device buffer that is refreshed before each replay.  The
         # reference does the same for its per-token decode (src/SharpInference.Engine/CudaForwardPass.cs:1668-1675).
         # Only models whose parts read the step through device tensors alone can be captured.
-        self.use_graphs = all(getattr(b.mixer, "graph_safe", False) and getattr(getattr(b, "ffn", None), "graph_safe", False)
-                              for b in model.blocks) if hasattr(model, "blocks") else False
+        self.use_graphs = (all(getattr(b.mixer, "graph_safe", False)
+                               and (getattr(b, "ffn", False) is None or getattr(getattr(b, "ffn", None), "graph_safe", False))
+                               for b in model.blocks)
+                           and all(getattr(op, "graph_safe", False) for op in getattr(model, "stream_ops", []))
+                           ) if hasattr(model, "blocks") else False
         self.max_graphs = 32
         self._graphs: Dict[tuple, dict] = {}
         self._graph_seen: set = set()
@@ -267,7 +273,8 @@ class StepRunner:
         self.validate(entries)
         self.cache.reserve([(e.request_id, len(e.tokens)) for e in entries])
         logits, done, num_tokens = None, False, sum(len(e.tokens) for e in entries)
-        if self.use_graphs and not (self.trace_router or self.trace_layers) and num_tokens == len(entries):
+        if (self.use_graphs and not (self.trace_router or self.trace_layers or self.trace_streams)
+                and num_tokens == len(entries)):
             done, logits = self._run_decode_graph(entries)
         if not done:
             ctx = self.build_context(entries)
@@ -275,9 +282,12 @@ class StepRunner:
                 ctx.extras["router_choices"] = []
             if self.trace_layers:
                 ctx.extras["layer_norms"] = []
+            if self.trace_streams:
+                ctx.extras["layer_streams"] = []
             logits = self.model.forward(ctx)
             self.last_router_choices = ctx.extras.get("router_choices", [])
             self.last_layer_norms = ctx.extras.get("layer_norms", [])
+            self.last_layer_streams = ctx.extras.get("layer_streams", [])
         if self.check_kernel_status:
             self._note_status()
         for e in entries:

@@ -33,7 +33,7 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_swiglu": ("elementwise", [P, P, P, P, I, I, I, P]),
     "sharpi_add": ("elementwise", [P, P, P, LL, P]),
     "sharpi_timestamp": ("elementwise", [P, I, P]),
-    "sharpi_qkv_post": ("rope_kv", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, I, P]),
+    "sharpi_qkv_post": ("rope_kv", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, I, I, P]),
     "sharpi_paged_attention_generic": ("attention_generic", [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_attention_decode": ("attention_decode", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P]),
     "sharpi_attention_prefill": ("attention_prefill", [P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),
@@ -51,6 +51,13 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_add_logit_bias": ("sampling", [P, I, P, P, P, I, P]),
     "sharpi_sample_rows": ("sampling", [P, I, I, P, P, P, P, P, P, P, P]),
     "sharpi_sample_rows_no_alloc": ("sampling", [P, I, I, P, P, P, P, P, P, P]),
+    "sharpi_bias_act": ("elementwise", [P, P, P, I, I, I, I, P]),
+    "sharpi_concat2": ("elementwise", [P, P, P, P, I, I, I, P]),
+    "sharpi_router_topk": ("moe_topk", [P, P, P, I, I, I, I, F, I, P, P, P, P]),
+    "sharpi_moe_pair_tokens": ("moe_topk", [P, I, I, P, P]),
+    "sharpi_moe_combine": ("moe_topk", [P, P, P, I, I, I, P]),
+    "sharpi_mlstm_recurrence": ("mlstm", [P, I, I, I, I, I, I, P, P, P, P, P, LL, I, I, I, I, I, I, F, F, P, P, P]),
+    "sharpi_mlstm_out": ("mlstm", [P, P, I, P, F, I, I, I, P, I, P]),
 }
 
 _libs: Dict[str, ctypes.CDLL] = {}

@@ -132,15 +132,52 @@ def add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) ->
     return out
 
 
+ACT_RELU2, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
+ACTIVATIONS = {"relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU}
+
+
+def bias_act(y: torch.Tensor, bias: Optional[torch.Tensor], act: int, out_dtype: torch.dtype,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(y + bias)`` over a float32 product ``[M, N]`` (``bias`` float32 ``[N]`` or None), in ``out_dtype``:
+    the square of relu, tanh-GELU or SiLU."""
+    _need(y, "y", torch.float32)
+    M, N = y.shape
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError(f"bias has {bias.numel()} entries, the rows have {N}")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=y.device)
+    check(kernel("sharpi_bias_act")(y.data_ptr(), _ptr(bias), out.data_ptr(), dtype_code(out.dtype), M, N, int(act),
+                                    _stream()), "sharpi_bias_act")
+    return out
+
+
+def concat2(a: torch.Tensor, delta: Optional[torch.Tensor], b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``[a + delta | b]`` row by row (float32 ``[T, H]`` each, ``delta`` may be None) as ``[T, 2H]`` in ``out_dtype``."""
+    _need(a, "a", torch.float32)
+    _need(b, "b", torch.float32)
+    if delta is not None:
+        _need(delta, "delta", torch.float32)
+    T, H = a.shape
+    if b.shape != a.shape or (delta is not None and delta.shape != a.shape):
+        raise KernelError(f"shapes differ: {tuple(a.shape)}, {tuple(b.shape)}")
+    out = torch.empty((T, 2 * H), dtype=out_dtype, device=a.device)
+    check(kernel("sharpi_concat2")(a.data_ptr(), _ptr(delta), b.data_ptr(), out.data_ptr(), dtype_code(out_dtype), T, H,
+                                   _stream()), "sharpi_concat2")
+    return out
+
+
 def qkv_post(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor,
              inv_freq: Optional[torch.Tensor], q_out: torch.Tensor, kv_layer: torch.Tensor, *, nq: int, nkv: int,
              d: int, page_size: int, pairing: int, l2_eps: float, temp_attn_scale: float, temp_floor_scale: float,
-             write_kv: bool) -> None:
+             write_kv: bool, l2_count: int = 0) -> None:
     """RoPE, per-head L2 norm, temperature factor, q store and K/V scatter into pages.
 
     ``qkv`` fp32 [T, (nq + 2 nkv) d]; ``kv_layer`` is one layer's pages
     ``[pages, 2, nkv, page_size, d]`` in the dtype of ``q_out``; ``l2_eps < 0`` and
-    ``temp_floor_scale <= 0`` switch the norm and the temperature factor off.
+    ``temp_floor_scale <= 0`` switch the norm and the temperature factor off.  ``l2_count`` (default ``d``) is the
+    number of elements the norm's mean of squares divides by: fewer than ``d`` when the heads are padded with zeros.
     """
     _need(qkv, "qkv", torch.float32)
     _need(positions, "positions", torch.int32)
@@ -161,7 +198,7 @@ def qkv_post(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, 
                                     block_table.data_ptr(), _ptr(inv_freq), q_out.data_ptr(), kv_layer.data_ptr(),
                                     dtype_code(q_out.dtype), T, nq, nkv, d, block_table.shape[-1], page_size,
                                     pairing, float(l2_eps), float(temp_attn_scale), float(temp_floor_scale),
-                                    int(write_kv), _stream()), "sharpi_qkv_post")
+                                    int(write_kv), int(l2_count), _stream()), "sharpi_qkv_post")
 
 
 def paged_attention_generic(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor,
@@ -595,6 +632,121 @@ def moe_sort(expert_id: torch.Tensor, num_experts: int):
     check(kernel("sharpi_moe_sort")(expert_id.data_ptr(), T, num_experts, offsets.data_ptr(),
                                     sorted_rows.data_ptr(), _stream()), "sharpi_moe_sort")
     return offsets, sorted_rows
+
+
+def router_topk(h32: torch.Tensor, router_weight: torch.Tensor, k: int, *, correction: Optional[torch.Tensor] = None,
+                scale: float = 1.0, renormalize: bool = False, want_scores: bool = False):
+    """Sigmoid routing to ``k`` experts a row.  ``s = sigmoid(h . Wr^T)`` in float32; the ``k`` largest of
+    ``s + correction`` are chosen (the lowest index among equals); the weights are ``scale * s`` of the chosen,
+    divided by their sum first when ``renormalize``.  Returns ``(expert_id int32 [T, k], weight float32 [T, k],
+    scores [T, E] or None)``."""
+    _need(h32, "h32", torch.float32)
+    _need(router_weight, "router_weight", torch.float32)
+    T, H = h32.shape
+    E = router_weight.shape[0]
+    if router_weight.shape[1] != H:
+        raise KernelError(f"router weight is {tuple(router_weight.shape)}, activations have width {H}")
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+        if correction.numel() != E:
+            raise KernelError(f"correction has {correction.numel()} entries for {E} experts")
+    if not (1 <= k <= min(E, 32)):
+        raise KernelError(f"experts per row must be 1 .. min(experts, 32), found {k} of {E}")
+    expert = torch.empty((T, k), dtype=torch.int32, device=h32.device)
+    weight = torch.empty((T, k), dtype=torch.float32, device=h32.device)
+    scores = torch.empty((T, E), dtype=torch.float32, device=h32.device) if want_scores else None
+    check(kernel("sharpi_router_topk")(h32.data_ptr(), router_weight.data_ptr(), _ptr(correction), T, H, E, k,
+                                       float(scale), int(renormalize), expert.data_ptr(), weight.data_ptr(),
+                                       _ptr(scores), _stream()), "sharpi_router_topk")
+    return expert, weight, scores
+
+
+def moe_pair_tokens(sorted_pairs: torch.Tensor, k: int) -> torch.Tensor:
+    """For (row, choice) pairs numbered ``row * k + choice`` and sorted by expert: the row of every sorted pair."""
+    _need(sorted_pairs, "sorted_pairs", torch.int32)
+    out = torch.empty_like(sorted_pairs)
+    check(kernel("sharpi_moe_pair_tokens")(sorted_pairs.data_ptr(), sorted_pairs.numel(), k, out.data_ptr(), _stream()),
+          "sharpi_moe_pair_tokens")
+    return out
+
+
+def moe_combine(y_pairs: torch.Tensor, k: int, *, add: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = add[t] + sum_j y_pairs[t * k + j]`` (float32), the choices added in their order."""
+    _need(y_pairs, "y_pairs", torch.float32)
+    P, H = y_pairs.shape
+    if P % k:
+        raise KernelError(f"{P} pair rows are no multiple of k = {k}")
+    T = P // k
+    if add is not None:
+        _need(add, "add", torch.float32)
+        if tuple(add.shape) != (T, H):
+            raise KernelError(f"add is {tuple(add.shape)}, expected {(T, H)}")
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=y_pairs.device)
+    _need(out, "out", torch.float32)
+    check(kernel("sharpi_moe_combine")(y_pairs.data_ptr(), _ptr(add), out.data_ptr(), T, k, H, _stream()),
+          "sharpi_moe_combine")
+    return out
+
+
+MLSTM_MAX_KEY_SIZE = 256
+
+
+def mlstm_state_floats(heads: int, d: int, dv: int):
+    """``(floats per head, floats per request)`` of the matrix-memory state: per head the value columns in slices of
+    32 ``[slices, d, 32]``, then the normaliser ``[d]``, then the running maximum (padded to four floats)."""
+    slices = (dv + 31) // 32
+    per_head = slices * d * 32 + d + 4
+    return per_head, heads * per_head
+
+
+def mlstm_recurrence(proj: torch.Tensor, *, col_q: int, col_k: int, col_v: int, col_i: int, col_f: int,
+                     bias_i: torch.Tensor, bias_f: torch.Tensor, row_offsets: torch.Tensor, state_slots: torch.Tensor,
+                     state: torch.Tensor, heads: int, d: int, dv: int, cap: float, q_scale: float) -> torch.Tensor:
+    """The matrix-memory recurrence over the step's rows (``mlstm.cu``): reads q, k, v and the raw gates from the
+    fused float32 projection ``proj [T, ld]`` at the given first columns, advances ``state [slots, floats]`` of
+    the step's requests (``state_slots [B]``, rows ``row_offsets [B + 1]``) and returns the unnormalised head
+    outputs, float32 ``[T, heads * dv]``."""
+    _need(proj, "proj", torch.float32)
+    _need(bias_i, "bias_i", torch.float32)
+    _need(bias_f, "bias_f", torch.float32)
+    _need(row_offsets, "row_offsets", torch.int32)
+    _need(state_slots, "state_slots", torch.int32)
+    _need(state, "state", torch.float32)
+    T, ld = proj.shape
+    B = state_slots.numel()
+    per_head, per_request = mlstm_state_floats(heads, d, dv)
+    if state.dim() != 2 or state.shape[1] != per_request:
+        raise KernelError(f"state is {tuple(state.shape)}, expected [slots, {per_request}]")
+    if d > MLSTM_MAX_KEY_SIZE:
+        raise KernelError(f"key size {d} is beyond the {MLSTM_MAX_KEY_SIZE} the recurrence kernels take")
+    if max(col_q + heads * d, col_k + heads * d, col_v + heads * dv, col_i + heads, col_f + heads) > ld:
+        raise KernelError("a part of the fused projection lies outside its columns")
+    coef = torch.empty((T, heads, 4), dtype=torch.float32, device=proj.device)
+    o_raw = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
+    check(kernel("sharpi_mlstm_recurrence")(proj.data_ptr(), ld, col_q, col_k, col_v, col_i, col_f, bias_i.data_ptr(),
+                                            bias_f.data_ptr(), row_offsets.data_ptr(), state_slots.data_ptr(),
+                                            state.data_ptr(), state.stride(0), per_head, B, T, heads, d, dv,
+                                            float(cap), float(q_scale), coef.data_ptr(), o_raw.data_ptr(), _stream()),
+          "sharpi_mlstm_recurrence")
+    return o_raw
+
+
+def mlstm_out(o_raw: torch.Tensor, proj: torch.Tensor, col_g: int, weight: torch.Tensor, eps: float, heads: int,
+              dv: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per head: ``o / rms(o) * weight * sigmoid(gate)`` with the gate read from ``proj[:, col_g:]``."""
+    _need(o_raw, "o_raw", torch.float32)
+    _need(proj, "proj", torch.float32)
+    _need(weight, "weight", torch.float32)
+    T = o_raw.shape[0]
+    if weight.numel() != heads * dv or o_raw.shape[1] != heads * dv or col_g + heads * dv > proj.shape[1]:
+        raise KernelError("head outputs, gate columns and norm weight disagree on heads * value size")
+    out = torch.empty((T, heads * dv), dtype=out_dtype, device=o_raw.device)
+    gate = proj[:, col_g:]
+    check(kernel("sharpi_mlstm_out")(o_raw.data_ptr(), gate.data_ptr(), proj.shape[1], weight.data_ptr(), float(eps), T,
+                                     heads, dv, out.data_ptr(), dtype_code(out_dtype), _stream()), "sharpi_mlstm_out")
+    return out
 
 
 _argmax_scratches = {}

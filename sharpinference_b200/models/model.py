@@ -15,7 +15,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from ..kernels import ops
-from ..parts.base import Block, Norm, StepContext
+from ..parts.base import Block, Norm, StepContext, StreamOp
 from ..parts.linear import Linear
 
 
@@ -23,14 +23,16 @@ from ..parts.linear import Linear
 class ScheduleEntry:
     layer: int                          # index into DecoderModel.blocks
     cache_from: Optional[int] = None    # schedule index whose cache this entry reads (no write of its own)
+    before: Optional[int] = None        # index into DecoderModel.stream_ops: run on the stream before this block
 
 
 class DecoderModel:
     def __init__(self, *, embedding: torch.Tensor, blocks: Sequence[Block], final_norm: Norm, head: Linear,
                  act_dtype: torch.dtype, schedule: Optional[Sequence[ScheduleEntry]] = None,
-                 eos_token_ids: Sequence[int] = (), config=None):
+                 eos_token_ids: Sequence[int] = (), config=None, stream_ops: Sequence[StreamOp] = ()):
         self.embedding = embedding                  # [V, H]
         self.blocks: List[Block] = list(blocks)
+        self.stream_ops: List[StreamOp] = list(stream_ops)
         self.final_norm = final_norm
         self.head = head
         self.act_dtype = act_dtype
@@ -51,6 +53,9 @@ class DecoderModel:
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.blocks)):
                 raise ValueError(f"schedule entry {i} names block {e.layer}; the model has {len(self.blocks)}")
+            if e.before is not None and not (0 <= e.before < len(self.stream_ops)):
+                raise ValueError(f"schedule entry {i} names stream operation {e.before}; the model has "
+                                 f"{len(self.stream_ops)}")
             if e.cache_from is not None:
                 if not (0 <= e.cache_from < i):
                     raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_from}, which must come earlier")
@@ -67,13 +72,21 @@ class DecoderModel:
         """Run the step's rows through every scheduled block; float32 logits ``[R, V]`` at
         ``ctx.want_rows`` (None if no logits are wanted)."""
         x = ops.embed_gather(ctx.token_ids, self.embedding)
+        # stream operations read the embedding output; the blocks add into x in place, so it is gathered twice
+        x0 = ops.embed_gather(ctx.token_ids, self.embedding) if self.stream_ops else None
         pending = None
         norms = ctx.extras.get("layer_norms")        # tracing: see StepRunner.trace_layers
+        streams = ctx.extras.get("layer_streams")    # tracing: the whole residual stream after every block
         for index, entry in enumerate(self.schedule):
+            if entry.before is not None:
+                x, pending = self.stream_ops[entry.before].forward(ctx, x, pending, x0)
             x, pending = self.blocks[entry.layer].forward(ctx, ctx.slots[index], x, pending)
-            if norms is not None:
+            if norms is not None or streams is not None:
                 after = x.float() if pending is None else x.float() + pending.float()
-                norms.append(after.square().sum(dim=1).sqrt())
+                if norms is not None:
+                    norms.append(after.square().sum(dim=1).sqrt())
+                if streams is not None:
+                    streams.append(after.clone())
         if ctx.want_rows is None or ctx.want_rows.numel() == 0:
             return None
         h, _ = self.final_norm.apply(x, pending, rows=ctx.want_rows, out_dtype=self.act_dtype)

@@ -1,14 +1,17 @@
 """Parts that layers are put together from: norms, position encodings, mixers, feed-forwards, blocks."""
 from .base import (Block, CacheSpec, FeedForward, LayerSlot, Mixer, Norm, Part, PositionEncoding, StateSpec,
-                   StepContext, make_part, part_kinds, register_part)
+                   StepContext, StreamOp, make_part, part_kinds, register_part)
 from .linear import GroupedLinear, Linear
 from .norm import L2Norm, RMSNorm
-from .position import NoPositionEncoding, RotaryEncoding, rotary_inv_freq
+from .position import NoPositionEncoding, RotaryEncoding, partial_rotary_inv_freq, rotary_inv_freq
 from .attention import PagedAttention
-from .feedforward import DenseSwiGLU, MoESigmoidTop1
-from .block import PreNormBlock
+from .mlstm import MLSTMMixer, fused_mlstm_columns
+from .feedforward import DenseMLP, DenseSwiGLU, MoESigmoidTop1, MoESigmoidTopK
+from .block import ParallelBlock, PreNormBlock
+from .stream import ReinjectInput
 
 __all__ = ["Block", "CacheSpec", "FeedForward", "LayerSlot", "Mixer", "Norm", "Part", "PositionEncoding",
            "StateSpec", "StepContext", "make_part", "part_kinds", "register_part", "GroupedLinear", "Linear",
            "L2Norm", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "rotary_inv_freq", "PagedAttention",
-           "DenseSwiGLU", "MoESigmoidTop1", "PreNormBlock"]
+           "DenseSwiGLU", "MoESigmoidTop1", "PreNormBlock", "StreamOp", "partial_rotary_inv_freq", "MLSTMMixer",
+           "fused_mlstm_columns", "DenseMLP", "MoESigmoidTopK", "ParallelBlock", "ReinjectInput"]

@@ -7,8 +7,14 @@ every row over the positions its mask lets it see; output projection.  Query hea
 kv head ``h // (heads / kv_heads)``; scores are ``q . k / sqrt(d)``.
 
 What the reference lacks is a parameter here: the mask (``full``, ``chunk`` of C positions,
-``window`` of W positions), and the temperature factor
-``1 + attn_scale * ln(1 + floor((pos + 1) / floor_scale))``.
+``window`` of W positions), the temperature factor
+``1 + attn_scale * ln(1 + floor((pos + 1) / floor_scale))``, the score factor (``softmax_scale``), and a value
+size that differs from the key size (``value_dim``).
+
+Unequal key and value sizes: the kernels and the pages know one head size, so the part pads both to a common
+size D once, when it is built: zero rows in the fused projection (a padded q, k or v element is an exact zero),
+zero columns in the output projection.  Zeros change neither a score nor a rotation (the padded pairs get
+frequency 0) nor an output, and the q/k norm divides its sum of squares by the key size, not by D.
 """
 from __future__ import annotations
 
@@ -72,26 +78,70 @@ class PagedAttentionPlanner(StepPlanner):
                     "decode_keys": keys if bucket is None else int(bucket)})
 
 
+def _pad_projections(qkv: Linear, out: Linear, nq: int, nkv: int, dk: int, dv: int, D: int):
+    """The fused q|k|v projection and the output projection with every head padded to ``D`` elements: zero rows
+    (and zero bias entries) behind each head of q, k and v, zero columns behind each head in ``out``."""
+    def pad_rows(block: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+        wide = torch.zeros((heads, D) + tuple(block.shape[1:]), dtype=block.dtype, device=block.device)
+        wide[:, :size] = block.reshape((heads, size) + tuple(block.shape[1:]))
+        return wide.reshape((heads * D,) + tuple(block.shape[1:]))
+
+    def pad_qkv(t: torch.Tensor) -> torch.Tensor:
+        q, k, v = t[: nq * dk], t[nq * dk: (nq + nkv) * dk], t[(nq + nkv) * dk:]
+        return torch.cat([pad_rows(q, nq, dk), pad_rows(k, nkv, dk), pad_rows(v, nkv, dv)]).contiguous()
+
+    w = out.weight
+    wide = torch.zeros((w.shape[0], nq, D), dtype=w.dtype, device=w.device)
+    wide[:, :, :dv] = w.reshape(w.shape[0], nq, dv)
+    return (Linear(pad_qkv(qkv.weight), qkv.name, stream_rows=qkv.stream_rows,
+                   bias=None if qkv.bias is None else pad_qkv(qkv.bias)),
+            Linear(wide.reshape(w.shape[0], nq * D).contiguous(), out.name, stream_rows=out.stream_rows, bias=out.bias,
+                   split_add_rows=out.split_add_rows))
+
+
 @register_part("mixer", "paged_attention")
 class PagedAttention(Mixer):
     def __init__(self, *, qkv: Linear, out: Linear, num_heads: int, num_kv_heads: int, head_dim: int,
                  mask: str = "full", span: int = 0, position: Optional[PositionEncoding] = None,
                  qk_norm: Optional[Norm] = None, qk_norm_first: bool = False,
                  temperature: Optional[Tuple[float, float]] = None,
-                 softmax_scale: Optional[float] = None, act_dtype: torch.dtype = torch.bfloat16):
+                 softmax_scale: Optional[float] = None, act_dtype: torch.dtype = torch.bfloat16,
+                 value_dim: Optional[int] = None):
         """``qk_norm``: any :class:`Norm` over the head size, applied to every head of q and k; after the
         position encoding (Llama 4's order) unless ``qk_norm_first``.  The weightless L2 norm after a rotation
         runs inside the kernel that rotates and writes the cache; every other combination applies the norm as
-        a launch of its own on q and on k."""
+        a launch of its own on q and on k.  ``value_dim``: the size of a value head when it is not ``head_dim``
+        (``qkv`` then has ``heads * head_dim + kv_heads * (head_dim + value_dim)`` rows and ``out`` reads
+        ``heads * value_dim`` columns)."""
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"heads ({num_heads}) must be a multiple of kv heads ({num_kv_heads})")
-        if head_dim % 2 != 0 or head_dim > 512:
-            raise ValueError(f"head size {head_dim} is not supported: it must be even and at most 512")
-        if qkv.out_features != (num_heads + 2 * num_kv_heads) * head_dim:
-            raise ValueError(f"fused qkv weight has {qkv.out_features} rows, expected "
-                             f"(heads + 2 kv_heads) * head_dim = {(num_heads + 2 * num_kv_heads) * head_dim}")
-        if out.in_features != num_heads * head_dim:
-            raise ValueError(f"output projection reads {out.in_features} columns, expected {num_heads * head_dim}")
+        key_dim = head_dim
+        value_dim = key_dim if value_dim is None else int(value_dim)
+        if key_dim <= 0 or value_dim <= 0 or key_dim % 2 != 0 or max(key_dim, value_dim) > 512:
+            raise ValueError(f"head sizes {key_dim} (keys) and {value_dim} (values) are not supported: the key size "
+                             f"must be even and both at most 512")
+        if qkv.out_features != (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim:
+            raise ValueError(f"fused qkv weight has {qkv.out_features} rows, expected (heads + kv_heads) * head_dim + "
+                             f"kv_heads * value_dim = {(num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim}")
+        if out.in_features != num_heads * value_dim:
+            raise ValueError(f"output projection reads {out.in_features} columns, expected {num_heads * value_dim}")
+        self.key_dim, self.value_dim = key_dim, value_dim
+        if value_dim != key_dim:
+            head_dim = max(key_dim, value_dim)
+            head_dim = (head_dim + 15) // 16 * 16 if head_dim <= 128 else head_dim + (head_dim & 1)
+            if qk_norm is not None and not (getattr(qk_norm, "fuses_into_rotation", False) and not qk_norm_first):
+                raise ValueError("with unequal key and value sizes only the weightless q/k norm after the position "
+                                 "encoding is built (a norm of its own launch would average over the padded size)")
+            if position is not None and position.rotary() is None:
+                raise ValueError("with unequal key and value sizes only rotary (or no) position encodings are built")
+            qkv, out = _pad_projections(qkv, out, num_heads, num_kv_heads, key_dim, value_dim, head_dim)
+            if position is not None:
+                inv_freq, pairing = position.rotary()
+                if pairing != "interleaved":
+                    raise ValueError("with unequal key and value sizes the rotation must pair neighbours")
+                wide = torch.zeros(head_dim // 2, dtype=inv_freq.dtype, device=inv_freq.device)
+                wide[: key_dim // 2] = inv_freq
+                position = type(position)(wide, pairing)
         self.qkv, self.out = qkv, out
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.cache_spec = CacheSpec(mask, span if mask != "full" else 0, num_kv_heads, head_dim)
@@ -107,7 +157,7 @@ class PagedAttention(Mixer):
                              f"weightless L2 norm fuses into the rotation kernel): place it before the position "
                              f"encoding (qk_norm_first=True) or use an encoding that edits q and k itself")
         self.temperature = temperature          # (attn_scale, floor_scale) or None
-        self.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(head_dim)
+        self.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(key_dim)
         self.act_dtype = act_dtype
         # an encoding that edits q and k itself may look at the step's host-side lists: no graph then
         self.graph_safe = position is None or position.rotary() is not None
@@ -155,7 +205,8 @@ class PagedAttention(Mixer):
         ops.qkv_post(qkv, ctx.positions, ctx.row_request, table, inv_freq, q, slot.kv, nq=nq, nkv=nkv, d=d,
                      page_size=slot.page_size, pairing=pairing,
                      l2_eps=self.qk_norm.eps if self._norm_fused else -1.0,
-                     temp_attn_scale=attn_scale, temp_floor_scale=floor_scale, write_kv=slot.writes_cache)
+                     temp_attn_scale=attn_scale, temp_floor_scale=floor_scale, write_kv=slot.writes_cache,
+                     l2_count=self.key_dim)
         mask_kind, mask_span = _MASK_CODE[self.cache_spec.kind], max(self.cache_spec.span, 1)
         if self.act_dtype == torch.bfloat16 and d in ops.FAST_ATTENTION_HEAD_SIZES:
             # tensor-core kernels: tiles of prompt rows, and single rows split over their keys

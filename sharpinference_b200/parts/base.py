@@ -194,6 +194,18 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamOp(Part):
+    """Something done to the residual stream between two scheduled blocks (a re-injection of the embedding
+    output before a pass over shared layers, for instance).  ``forward(ctx, x, pending, x0) -> (x, pending)``:
+    ``x`` is the float32 residual stream, ``pending`` a float32 update not yet added to it (or None), ``x0`` the
+    embedding output of the step's rows (float32, never written)."""
+
+    graph_safe = False
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, pending: Optional[torch.Tensor], x0: torch.Tensor):
+        raise NotImplementedError
+
+
 class Block(Part):
     mixer: Mixer
 
@@ -207,7 +219,7 @@ class Block(Part):
 # Registry of part kinds
 # ---------------------------------------------------------------------------------------
 _PARTS: Dict[str, Dict[str, Callable[..., Part]]] = {
-    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {},
+    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}, "stream": {},
 }
 
 

@@ -4,6 +4,10 @@
 ``x += mixer(norm1(x))``, then ``x += ffn(norm2(x))``.  The residual stream is float32; each
 residual add is fused into the norm that follows it, so a block returns its feed-forward output
 as ``pending`` and the next block's first norm (or the model's last) adds it.
+
+``ParallelBlock`` has one norm whose output both sublayers read: ``h = norm(x)``,
+``x += mixer(h) + ffn(h)``; the feed-forward may be absent.  The sum of the two outputs is the
+``pending`` update.
 """
 from __future__ import annotations
 
@@ -11,6 +15,7 @@ from typing import Optional
 
 import torch
 
+from ..kernels import ops
 from .base import Block, FeedForward, LayerSlot, Mixer, Norm, StepContext, register_part
 
 
@@ -27,3 +32,20 @@ class PreNormBlock(Block):
         h, h32 = self.ffn_norm.apply(x, mixed, rows=None, out_dtype=self.act_dtype,
                                      want_fp32=self.ffn.wants_fp32_input)
         return x, self.ffn.forward(ctx, h, h32)
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Block):
+    def __init__(self, *, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward], act_dtype: torch.dtype = torch.bfloat16):
+        self.norm, self.mixer, self.ffn = norm, mixer, ffn
+        self.act_dtype = act_dtype
+
+    def forward(self, ctx: StepContext, slot: LayerSlot, x: torch.Tensor, pending: Optional[torch.Tensor]):
+        want32 = self.ffn is not None and self.ffn.wants_fp32_input
+        h, h32 = self.norm.apply(x, pending, rows=None, out_dtype=self.act_dtype, want_fp32=want32)
+        mixed = self.mixer.forward(ctx, slot, h)
+        if self.ffn is None:
+            return x, mixed
+        if getattr(self.ffn, "adds_to", False):          # the feed-forward's last kernel adds the mixer's output in
+            return x, self.ffn.forward(ctx, h, h32, add_to=mixed)
+        return x, ops.add(mixed, self.ffn.forward(ctx, h, h32), out=mixed)

@@ -1,5 +1,6 @@
-"""Feed-forward parts: dense SwiGLU, and a top-1 sigmoid-routed mixture of experts with an
-always-on shared expert.
+"""Feed-forward parts: dense SwiGLU, a top-1 sigmoid-routed mixture of experts with an
+always-on shared expert, a dense two-layer network with a plain activation (``DenseMLP``) and a
+sigmoid-routed mixture in which every row uses k such networks (``MoESigmoidTopK``).
 
 Dense (src/SharpInference.Engine/ForwardPass.cs:2006-2015): ``y = (silu(h Wg^T) * (h Wu^T)) Wd^T``.
 
@@ -155,3 +156,98 @@ class MoESigmoidTop1(FeedForward):
             main.wait_stream(side)
         self.experts_down(act, offsets, rows=T, out_rows=sorted_rows, out=y, accumulate=True)
         return y
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseMLP(FeedForward):
+    """``W_down act(W_up h + b_up) + b_down`` with ``act`` one of ``ops.ACTIVATIONS`` (the square of relu,
+    tanh-GELU, SiLU); the biases are optional.  The bias of the first product and the activation are one kernel
+    over the product's float32 result."""
+
+    graph_safe = True
+    adds_to = True
+
+    def __init__(self, *, up: Linear, down: Linear, activation: str = "relu2", act_dtype: torch.dtype = torch.bfloat16):
+        if up.out_features != down.in_features:
+            raise ValueError(f"up projection has {up.out_features} rows, down projection reads {down.in_features}")
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation '{activation}' is not one of {', '.join(sorted(ops.ACTIVATIONS))}")
+        # the first product leaves its bias to the activation kernel
+        self.up = Linear(up.weight, up.name, stream_rows=up.stream_rows)
+        self.up_bias = up.bias
+        self.down, self.activation, self.act_dtype = down, activation, act_dtype
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None,
+                add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
+        act = ops.bias_act(self.up(h), self.up_bias, ops.ACTIVATIONS[self.activation], self.act_dtype)
+        y = self.down(act)
+        return y if add_to is None else ops.add(add_to, y, out=add_to)
+
+
+@register_part("feed_forward", "moe_sigmoid_topk")
+class MoESigmoidTopK(FeedForward):
+    """A mixture of ``E`` two-layer experts (``W_down act(W_up h)``, no biases) of which every row uses ``top_k``.
+
+    Router: ``s = sigmoid(Wr h)`` in float32 on the unrounded activations; the ``top_k`` experts with the largest
+    ``s + correction`` are chosen (``correction`` may be None; the lowest index wins among equals); an expert's
+    output is weighted by ``route_scale * s`` (without the correction), the chosen ``s`` divided by their sum
+    first when ``renormalize``.  The (row, choice) pairs are sorted by expert on the device; each expert multiplies
+    its rows in one grouped product (tcgen05 for bfloat16 weights whose inner sizes are multiples of 8, CUDA cores
+    otherwise), the second product scales each pair's row by its weight, and the pairs of a row are added in the
+    order of the choices, so a row's result does not depend on the rest of the step.
+
+    The reference's mixture (src/SharpInference.Engine/ForwardPass.cs:2021-2098) is top-1 with a shared expert.
+    """
+
+    wants_fp32_input = True
+    graph_safe = True
+    adds_to = True
+
+    def __init__(self, *, router: torch.Tensor, experts_up: GroupedLinear, experts_down: GroupedLinear, top_k: int,
+                 correction: Optional[torch.Tensor] = None, route_scale: float = 1.0, renormalize: bool = False,
+                 activation: str = "relu2", act_dtype: torch.dtype = torch.bfloat16):
+        E = experts_up.num_groups
+        if router.shape != (E, experts_up.in_features):
+            raise ValueError(f"router weight is {tuple(router.shape)}, expected [{E}, {experts_up.in_features}]")
+        if experts_down.num_groups != E or experts_up.out_features != experts_down.in_features:
+            raise ValueError("expert up and down weights disagree on the number or width of the experts")
+        if not (1 <= top_k <= min(E, 32)):
+            raise ValueError(f"experts per row must be 1 .. min(experts, 32), found {top_k} of {E}")
+        if correction is not None and correction.numel() != E:
+            raise ValueError(f"router correction has {correction.numel()} entries for {E} experts")
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation '{activation}' is not one of {', '.join(sorted(ops.ACTIVATIONS))}")
+        self.router, self.correction = router, correction
+        self.experts_up, self.experts_down = experts_up, experts_down
+        self.num_experts, self.top_k = E, int(top_k)
+        self.route_scale, self.renormalize = float(route_scale), bool(renormalize)
+        self.activation, self.act_dtype = activation, act_dtype
+        self._tensor_core = (experts_up.weight.dtype == torch.bfloat16 and experts_down.weight.dtype == torch.bfloat16
+                             and act_dtype == torch.bfloat16 and experts_up.in_features % 8 == 0
+                             and experts_down.in_features % 8 == 0)
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None,
+                add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T, k = h.shape[0], self.top_k
+        if h32 is None:
+            h32 = h.to(torch.float32)
+        expert, weight, _ = ops.router_topk(h32, self.router, k, correction=self.correction, scale=self.route_scale,
+                                            renormalize=self.renormalize)
+        if "router_choices" in ctx.extras:          # tracing: which experts every row went to
+            ctx.extras["router_choices"].append(expert)
+        offsets, sorted_pairs = ops.moe_sort(expert.view(-1), self.num_experts)     # pair = row * k + choice
+        pair_rows = ops.moe_pair_tokens(sorted_pairs, k) if k > 1 else sorted_pairs
+        act_code = ops.ACTIVATIONS[self.activation]
+        y = torch.empty((T * k, self.experts_down.out_features), dtype=torch.float32, device=h.device)
+        if self._tensor_core and h.dtype == torch.bfloat16:
+            h_sorted = ops.gather_rows_bf16(h, pair_rows)
+            up = ops.tc_grouped_gemm(h_sorted, self.experts_up.weight, offsets, mode=ops.TC_MODE_STORE)
+            act = ops.bias_act(up, None, act_code, torch.bfloat16)
+            ops.tc_grouped_gemm(act, self.experts_down.weight, offsets, mode=ops.TC_MODE_STORE, out=y,
+                                out_rows=sorted_pairs, row_scale=weight.view(-1), scale_rows=sorted_pairs)
+        else:
+            up = self.experts_up(h, offsets, rows=T * k, a_rows=pair_rows)             # sorted order
+            act = ops.bias_act(up, None, act_code, self.act_dtype)
+            ops.gemm_nt(act, self.experts_down.weight, out=y, group_offsets=offsets, out_rows=sorted_pairs, rows=T * k,
+                        row_scale=weight.view(-1), scale_rows=sorted_pairs)
+        return ops.moe_combine(y, k, add=add_to, out=add_to)

@@ -2,7 +2,8 @@
 
 RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w`` (src/SharpInference.Cpu/SimdKernels.cs:4209-4246);
 the weightless form drops ``w`` (src/SharpInference.Cpu/SimdKernels.cs:4252-4283).  The sum of
-squares, the rsqrt and the scaling are float32.
+squares, the rsqrt and the scaling are float32.  Models that store the weight around zero and scale by
+``1 + w`` pass ``unit_offset=True``: the sum is formed once, in float32, when the part is built.
 """
 from __future__ import annotations
 
@@ -14,9 +15,10 @@ from .base import Norm, register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, weight: torch.Tensor, eps: float):
-        self.weight = weight
+    def __init__(self, weight: torch.Tensor, eps: float, unit_offset: bool = False):
+        self.weight = (weight.to(torch.float32) + 1.0) if unit_offset else weight
         self.eps = float(eps)
+        self.unit_offset = bool(unit_offset)
 
     def apply(self, x, delta, *, rows=None, out_dtype=torch.bfloat16, want_fp32=False):
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, out_dtype, rows=rows, want_fp32=want_fp32)

@@ -57,6 +57,19 @@ def rotary_inv_freq(head_dim: int, theta: float, scaling=None) -> torch.Tensor:
     return out
 
 
+def partial_rotary_inv_freq(head_dim: int, rot_dims: int, base: float) -> torch.Tensor:
+    """float32 ``[head_dim / 2]`` frequencies of a rotation that turns only the first ``rot_dims`` elements of a
+    head: pair ``j < rot_dims / 2`` gets ``base^(-2j / rot_dims)`` (formed in float64, rounded once), the pairs
+    beyond get 0, which is the rotation by no angle: those elements pass unchanged, bit for bit."""
+    if rot_dims % 2 or not (0 <= rot_dims <= head_dim) or head_dim % 2:
+        raise ValueError(f"rotated size {rot_dims} must be even and at most the (even) head size {head_dim}")
+    out = torch.zeros(head_dim // 2, dtype=torch.float64)
+    if rot_dims:
+        j = torch.arange(rot_dims // 2, dtype=torch.float64)
+        out[: rot_dims // 2] = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * j / float(rot_dims))
+    return out.to(torch.float32)
+
+
 @register_part("position", "rotary")
 class RotaryEncoding(PositionEncoding):
     def __init__(self, inv_freq: torch.Tensor, pairing: str = "interleaved"):
