@@ -5,6 +5,10 @@
     python bench_kernels.py attention_decode --batch 64 --context 8192
     python bench_kernels.py attention_prefill --tokens 2048
     python bench_kernels.py dense --rows 8 --n 7168 --k 5120 --impl grouped
+    python bench_kernels.py mlstm --batch 64 --tokens 1            (decode: the state streams through once)
+    python bench_kernels.py mlstm --batch 1 --tokens 2048          (a prompt portion: float32 FMA work)
+    python bench_kernels.py router_topk --tokens 2048 --experts 16 --top 2
+    python bench_kernels.py mixture_glue --tokens 2048             (activation, pair rows, combine)
 
 Each run warms the kernel up, times ``--iters`` launches with CUDA events and prints one line with
 the time per launch and the achieved bytes or flops per second.  The inputs are larger than the L2
@@ -154,6 +158,84 @@ def router(ns) -> None:
           f"{(T * H * 4 + E * H * 4) / ms / 1e6:.0f} GB/s of activations and router rows read once")
 
 
+def mlstm(ns) -> None:
+    """The matrix-memory recurrence (gates, scan, head norm) for `batch` requests of `tokens` rows each.  Decode
+    (tokens = 1) is a stream of the state: read and written once.  A prompt portion is float32 FMA work: per row and
+    head 4 d dv flops (the update of S and S^T q)."""
+    from sharpinference_b200.parts.mlstm import fused_mlstm_columns
+    B, n, heads, d, dv = ns.batch, ns.tokens, ns.heads, ns.key_dim, ns.value_dim
+    cq, ck, cv, cg, ci, cf, width = fused_mlstm_columns(heads, d, dv)
+    T = B * n
+    proj = torch.randn(T, width, device=DEV)
+    proj[:, cf:cf + heads] += 3.0
+    bias = torch.zeros(heads, device=DEV)
+    w = torch.ones(heads * dv, device=DEV)
+    per_head, per_request = ops.mlstm_state_floats(heads, d, dv)
+    copies = max(1, (300 << 20) // (B * per_request * 4) + 1) if n == 1 else 1
+    state = torch.zeros(copies * B, per_request, device=DEV)
+    offs = torch.arange(0, T + 1, n, dtype=torch.int32, device=DEV)
+    slot_sets = [torch.arange(c * B, (c + 1) * B, dtype=torch.int32, device=DEV) for c in range(copies)]
+    it = {"i": 0}
+
+    def fn():
+        slots = slot_sets[it["i"] % copies]
+        it["i"] += 1
+        num, nq, coef = ops.mlstm_recurrence(proj, col_q=cq, col_k=ck, col_v=cv, col_i=ci, col_f=cf, bias_i=bias, bias_f=bias,
+                                 row_offsets=offs, state_slots=slots, state=state, heads=heads, d=d, dv=dv, cap=15.0,
+                                 q_scale=d ** -0.5)
+        ops.mlstm_out(num, nq, coef, proj, cg, w, 1e-5, heads, dv, torch.bfloat16)
+    ms = _time(fn, max(ns.iters, copies))
+    state_bytes = 2 * B * per_request * 4
+    flops = 4.0 * T * heads * d * dv
+    print(f"mlstm batch={B} tokens={n} heads={heads} d={d} dv={dv}: {ms * 1e3:.1f} us, state {state_bytes / ms / 1e6:.0f} GB/s "
+          f"(read and written once), {flops / ms / 1e9:.2f} TFLOP/s float32")
+
+
+def router_topk(ns) -> None:
+    T, H, E = ns.tokens, ns.hidden, ns.experts
+    copies = max(2, (300 << 20) // (T * H * 4) + 1)
+    hs = [torch.randn(T, H, device=DEV) for _ in range(copies)]
+    wr = torch.randn(E, H, device=DEV) * 0.05
+    corr = torch.randn(E, device=DEV) * 0.1
+    it = {"i": 0}
+
+    def fn():
+        ops.router_topk(hs[it["i"] % copies], wr, ns.top, correction=corr, scale=2.5)
+        it["i"] += 1
+    ms = _time(fn, max(ns.iters, copies))
+    print(f"router_topk tokens={T} hidden={H} experts={E} top={ns.top}: {ms * 1e3:.1f} us, "
+          f"{(T * H * 4 + E * H * 4) / ms / 1e6:.0f} GB/s of activations and router rows read once")
+
+
+def mixture_glue(ns) -> None:
+    """What stands between the grouped products of a top-k mixture: the activation over the first product, the rows
+    of the sorted pairs, and the sum of a row's pairs."""
+    T, H, I, k, E = ns.tokens, ns.hidden, ns.inter, ns.top, ns.experts
+    P = T * k
+    copies = max(2, (300 << 20) // (P * max(I, H) * 4) + 1)
+    ups = [torch.randn(P, I, device=DEV) for _ in range(copies)]
+    ys = [torch.randn(P, H, device=DEV) for _ in range(copies)]
+    add = torch.randn(T, H, device=DEV)
+    expert = torch.randint(0, E, (P,), device=DEV, dtype=torch.int32)
+    it = {"i": 0}
+
+    def act():
+        ops.bias_act(ups[it["i"] % copies], None, ops.ACT_RELU2, torch.bfloat16)
+        it["i"] += 1
+
+    def combine():
+        ops.moe_combine(ys[it["i"] % copies], k, add=add, out=add)
+        it["i"] += 1
+
+    def sort():
+        _, pairs = ops.moe_sort(expert, E)
+        ops.moe_pair_tokens(pairs, k)
+    for name, fn, nbytes in (("bias_act relu2", act, P * I * 6), ("moe_combine", combine, P * H * 4 + 2 * T * H * 4),
+                             ("moe_sort + pair_tokens", sort, P * 12)):
+        ms = _time(fn, max(ns.iters, copies))
+        print(f"{name} tokens={T} top={k}: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s")
+
+
 def elementwise(ns) -> None:
     """The memory-bound kernels between the products of a prompt step, each call on another copy of its inputs
     (copies that exceed L2 together), with the bytes each has to move."""
@@ -223,7 +305,7 @@ def attention_decode(ns) -> None:
         positions[1:] = min(ns.others_context, S) - 1
     row_req = torch.arange(B, dtype=torch.int32, device=DEV)
     out = torch.empty(B, nq * d, dtype=torch.bfloat16, device=DEV)
-    kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK}[ns.mask]
+    kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK, "window": ops.MASK_WINDOW}[ns.mask]
     keys = int((positions.long() + 1).sum())
     fn = lambda: ops.attention_decode(q, kv, table, row_req, positions, out, rows=None, num_rows=B, nq=nq, nkv=nkv, d=d,
                                       page_size=ps, mask_kind=kind, mask_span=ns.span, scale=1 / math.sqrt(d),
@@ -241,7 +323,7 @@ def attention_prefill(ns) -> None:
     rows = 64 if ns.warp_mma else ops.TC_PREFILL_TILE
     tiles = torch.tensor([[t0, min(rows, T - t0), start + t0, 0] for t0 in range(0, T, rows)], dtype=torch.int32, device=DEV)
     out = torch.empty(T, nq * d, dtype=torch.bfloat16, device=DEV)
-    kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK}[ns.mask]
+    kind = {"full": ops.MASK_FULL, "chunk": ops.MASK_CHUNK, "window": ops.MASK_WINDOW}[ns.mask]
     kernel = ops.attention_prefill if ns.warp_mma else ops.attention_prefill_tc
     fn = lambda: kernel(q, kv, table, tiles, out, nq=nq, nkv=nkv, d=d, page_size=ps, mask_kind=kind,
                         mask_span=ns.span, scale=1 / math.sqrt(d))
@@ -292,6 +374,21 @@ def main(argv=None) -> int:
     p.add_argument("--hidden", type=int, default=5120)
     p.add_argument("--experts", type=int, default=16)
     p.set_defaults(fn=router)
+    p = sub.add_parser("mlstm")
+    p.add_argument("--batch", type=int, default=64)
+    p.add_argument("--tokens", type=int, default=1)
+    p.add_argument("--heads", type=int, default=8)
+    p.add_argument("--key-dim", type=int, default=128)
+    p.add_argument("--value-dim", type=int, default=256)
+    p.set_defaults(fn=mlstm)
+    for name, fn in (("router_topk", router_topk), ("mixture_glue", mixture_glue)):
+        p = sub.add_parser(name)
+        p.add_argument("--tokens", type=int, default=2048)
+        p.add_argument("--hidden", type=int, default=2048)
+        p.add_argument("--inter", type=int, default=1024)
+        p.add_argument("--experts", type=int, default=16)
+        p.add_argument("--top", type=int, default=2)
+        p.set_defaults(fn=fn)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)
@@ -304,7 +401,7 @@ def main(argv=None) -> int:
         p.add_argument("--kv-heads", type=int, default=8)
         p.add_argument("--head-dim", type=int, default=128)
         p.add_argument("--page-size", type=int, default=64)
-        p.add_argument("--mask", choices=["full", "chunk"], default="full")
+        p.add_argument("--mask", choices=["full", "chunk", "window"], default="full")
         p.add_argument("--span", type=int, default=8192)
         p.add_argument("--warp-mma", action="store_true", help="attention_prefill: the m16n8k16 kernel with 64-row tiles")
         p.set_defaults(fn=fn)

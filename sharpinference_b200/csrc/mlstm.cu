@@ -15,26 +15,32 @@
 // by a weight and by sigmoid of an output gate.
 //
 // Three kernels, all reading the step through device arrays only (row_offsets, state_slots):
-//   gates   one warp per (request, head) walks the request's rows in order: gates, m, a, b, n and the denominator;
-//           it owns n and m of the state.  The next row's operands are loaded while this row is computed.
-//   scan    one CTA per (request, head, slice of 32 value columns) walks the rows in order with its [d, 32] slice
-//           of S in registers (warp w holds a band of rows, lane l column l); keys, queries and coefficients of
-//           MLSTM_CHUNK rows at a time are staged in shared memory, and the bands' partial sums of S^T q meet there.
-//           A row's result is one fixed sequence of operations, whatever the portion it arrived in.
-//   out     one warp per (row, head): root mean square over dv, weight, output gate.
+//   gates   one warp per (request, head) walks the request's rows in order, 32 at a time: lane j forms the capped
+//           gates of row j (tanh, logsigmoid), then every lane runs the same 32 steps of m_t = max(f_t + m_{t-1}, i_t)
+//           on values handed round by shuffles (one addition and one maximum a row on the serial path), and lane j
+//           leaves log a_t, log b_t and m_t of its row.  It owns m of the state.
+//   scan    one CTA of 128 threads per (request, head, slice of 32 value columns) walks the rows in order with its
+//           [d, 32] slice of S in registers: a thread holds d / 16 rows of four neighbouring columns, so that every
+//           key and query element it reads from shared memory serves four columns.  The normaliser n is one more
+//           slice whose "value" is 1 in its first column and 0 elsewhere, so n . q comes out of the same code as
+//           S^T q and no CTA reads what another writes.  Keys, queries and coefficients of a chunk of rows at a time
+//           are staged in shared memory (the next chunk's are on their way in registers meanwhile), and the 16
+//           partial sums of every (row, column) meet there.  A row's result is one fixed sequence of operations,
+//           whatever the portion it arrived in.
+//   out     one warp per (row, head): the division by max(|n . q|, exp(-m)) + 1e-6, then root mean square over dv,
+//           weight, output gate.
 //
-// State of one request and layer: per head [slices][d][32] floats of S (value columns padded with zeros to whole
-// slices), then n [d], then m and three unused floats; `head_stride` floats per head.
+// State of one request and layer, per head: for every slice of 32 value columns [d][32] floats of S (columns beyond
+// dv are zeros), then n [d], then m and three unused floats.  `head_stride` floats per head.
 #include "common.cuh"
 
-constexpr int MLSTM_CHUNK = 16;      // rows staged in shared memory at a time
-constexpr int MLSTM_WARPS = 8;       // warps of a scan CTA (bands of state rows)
+constexpr int MLSTM_CHUNK = 8;       // rows staged in shared memory at a time (half as many at the largest key size)
 constexpr int MLSTM_MAX_D = 256;     // key/query size the kernels take
 
 struct MlstmArgs {
     const float* proj;       // [T, ld] fused projections of the step's rows
     int ld;
-    int col_q, col_k, col_v, col_g, col_i, col_f;    // first column of each part (heads * size each)
+    int col_q, col_k, col_v, col_i, col_f;    // first column of each part (heads * size each)
     const float* bias_i;     // [heads]
     const float* bias_f;     // [heads]
     const int* row_offsets;  // [B + 1] first row of every request
@@ -44,8 +50,9 @@ struct MlstmArgs {
     int head_stride;         // floats per head inside a slot
     int heads, d, dv, slices;
     float cap, q_scale;
-    float* coef;             // [T, heads, 4]: a, b, denominator, unused
-    float* o_raw;            // [T, heads * dv]
+    float* coef;             // [T, heads, 4]: log a, log b, m, unused
+    float* o_raw;            // [T, heads * dv]: S^T q, not yet divided
+    float* nq;               // [T, heads]: n . q
 };
 
 __device__ __forceinline__ float log_sigmoid(float x) {
@@ -56,188 +63,211 @@ __device__ __forceinline__ float log_sigmoid(float x) {
 // ---------------------------------------------------------------------------------------
 // gates: grid (B, heads), one warp
 // ---------------------------------------------------------------------------------------
-template <int PER_LANE>
 __global__ void __launch_bounds__(32) mlstm_gates_kernel(MlstmArgs a) {
     const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
     const int r0 = a.row_offsets[b], r1 = a.row_offsets[b + 1];
     if (r1 <= r0) return;
-    float* st = a.state + (size_t)a.state_slots[b] * a.state_stride + (size_t)h * a.head_stride;
-    float* n_state = st + (size_t)a.slices * a.d * 32;
-    float* m_state = n_state + a.d;
-    const int d = a.d;
-    float n[PER_LANE];
-#pragma unroll
-    for (int j = 0; j < PER_LANE; ++j) {
-        const int c = lane + 32 * j;
-        n[j] = c < d ? n_state[c] : 0.0f;
-    }
+    float* m_state = a.state + (size_t)a.state_slots[b] * a.state_stride + (size_t)h * a.head_stride +
+                     (size_t)a.slices * a.d * 32 + a.d;
     float m = *m_state;
     const float bi = a.bias_i[h], bf = a.bias_f[h];
-
-    float kq[2][PER_LANE], qq[2][PER_LANE], zi[2], zf[2];
-    auto fetch = [&](int r, int buf) {
-        const float* row = a.proj + (size_t)r * a.ld;
-#pragma unroll
-        for (int j = 0; j < PER_LANE; ++j) {
-            const int c = lane + 32 * j;
-            kq[buf][j] = c < d ? row[a.col_k + h * d + c] : 0.0f;
-            qq[buf][j] = c < d ? row[a.col_q + h * d + c] : 0.0f;
-        }
-        zi[buf] = row[a.col_i + h];
-        zf[buf] = row[a.col_f + h];
-    };
-    fetch(r0, 0);
-    for (int r = r0; r < r1; ++r) {
-        const int cur = (r - r0) & 1;
-        if (r + 1 < r1) fetch(r + 1, cur ^ 1);
-        const float ig = a.cap * tanhf((zi[cur] + bi) / a.cap);
-        const float fg = log_sigmoid(a.cap * tanhf((zf[cur] + bf) / a.cap));
-        const float m_new = fmaxf(fg + m, ig);
-        const float ca = expf(fg + m - m_new);
-        const float cb = expf(ig - m_new);
-        float dot = 0.0f;
-#pragma unroll
-        for (int j = 0; j < PER_LANE; ++j) {
-            n[j] = fmaf(ca, n[j], cb * kq[cur][j]);
-            dot = fmaf(n[j], qq[cur][j] * a.q_scale, dot);
-        }
-        dot = warp_sum(dot);
-        m = m_new;
-        if (lane == 0) {
-            float* c = a.coef + ((size_t)r * a.heads + h) * 4;
-            c[0] = ca;
-            c[1] = cb;
-            c[2] = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
-        }
+    float zi = 0.0f, zf = 0.0f;
+    if (r0 + lane < r1) {
+        zi = a.proj[(size_t)(r0 + lane) * a.ld + a.col_i + h];
+        zf = a.proj[(size_t)(r0 + lane) * a.ld + a.col_f + h];
     }
-#pragma unroll
-    for (int j = 0; j < PER_LANE; ++j) {
-        const int c = lane + 32 * j;
-        if (c < d) n_state[c] = n[j];
+    for (int t0 = r0; t0 < r1; t0 += 32) {
+        const int n = min(32, r1 - t0);
+        const float ig = a.cap * tanhf((zi + bi) / a.cap);
+        const float fg = log_sigmoid(a.cap * tanhf((zf + bf) / a.cap));
+        if (t0 + 32 + lane < r1) {                       // the next 32 rows' raw gates, while these are walked
+            zi = a.proj[(size_t)(t0 + 32 + lane) * a.ld + a.col_i + h];
+            zf = a.proj[(size_t)(t0 + 32 + lane) * a.ld + a.col_f + h];
+        }
+        float m_before = 0.0f, m_after = 0.0f;
+        for (int j = 0; j < n; ++j) {
+            const float fj = __shfl_sync(0xffffffffu, fg, j), ij = __shfl_sync(0xffffffffu, ig, j);
+            const float m_new = fmaxf(fj + m, ij);
+            if (lane == j) { m_before = m; m_after = m_new; }
+            m = m_new;
+        }
+        if (lane < n) {
+            float* c = a.coef + ((size_t)(t0 + lane) * a.heads + h) * 4;
+            c[0] = fg + m_before - m_after;
+            c[1] = ig - m_after;
+            c[2] = m_after;
+        }
     }
     if (lane == 0) *m_state = m;
 }
 
 // ---------------------------------------------------------------------------------------
-// scan: grid (B, heads, slices), MLSTM_WARPS warps; warp w holds state rows [w * BAND, (w + 1) * BAND)
+// scan: grid (B, heads, slices + 1), 128 threads.  Thread (warp w, group g, column group c; lane = 8 g + c) holds
+// rows (4 w + g) * RT .. + RT - 1 of columns 4 c .. 4 c + 3 of its slice.
 // ---------------------------------------------------------------------------------------
-template <int BAND>
-__global__ void __launch_bounds__(MLSTM_WARPS * 32) mlstm_scan_kernel(MlstmArgs a) {
-    extern __shared__ float smem[];
+constexpr int SCAN_THREADS = 128;
+
+// One float from global to shared memory without passing through a register; `take` = false writes a zero.
+__device__ __forceinline__ void copy_async_f32(float* dst_shared, const float* src, bool take) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(dst_shared);
+    const int bytes = take ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int RT>
+__global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a) {
+    constexpr int DP = RT * 16;                         // padded key size
+    constexpr int CHUNK = RT >= 16 ? MLSTM_CHUNK / 2 : MLSTM_CHUNK;      // rows staged at a time (48 KB of shared memory)
+    constexpr int PER_THREAD = (CHUNK * DP) / SCAN_THREADS;              // staged k (and q) floats per thread
+    constexpr int V_PER_THREAD = (CHUNK * 32) / SCAN_THREADS;
+    // two stages: while one chunk of rows is walked, the next one's keys, queries, values and coefficients arrive
+    __shared__ __align__(16) float k_s[2][CHUNK * DP];
+    __shared__ __align__(16) float q_s[2][CHUNK * DP];
+    __shared__ __align__(16) float v_s[2][CHUNK * 32];
+    __shared__ float c_s[2][CHUNK * 2];                 // log a, log b
+    __shared__ __align__(16) float p_s[CHUNK * 16 * 32];      // [row][4 w + g][column]
     const int b = blockIdx.x, h = blockIdx.y, slice = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wg = warp * 4 + (lane >> 3), c4 = (lane & 7) * 4;
     const int r0 = a.row_offsets[b], r1 = a.row_offsets[b + 1];
     if (r1 <= r0) return;
     const int d = a.d, dv = a.dv;
-    constexpr int DP = BAND * MLSTM_WARPS;              // padded key size
-    float* k_s = smem;                                  // [CHUNK][DP]
-    float* q_s = k_s + MLSTM_CHUNK * DP;                // [CHUNK][DP]
-    float* v_s = q_s + MLSTM_CHUNK * DP;                // [CHUNK][32]
-    float* c_s = v_s + MLSTM_CHUNK * 32;                // [CHUNK][4]
-    float* p_s = c_s + MLSTM_CHUNK * 4;                 // [CHUNK][WARPS][32]
-
-    float* st = a.state + (size_t)a.state_slots[b] * a.state_stride + (size_t)h * a.head_stride +
-                (size_t)slice * d * 32;
-    const int row0 = warp * BAND;
-    float S[BAND];
+    const bool norm_slice = slice == a.slices;          // the slice that carries n in its first column
+    float* head = a.state + (size_t)a.state_slots[b] * a.state_stride + (size_t)h * a.head_stride;
+    float* st = head + (size_t)slice * d * 32;          // value slices: [d][32]; the normaliser: [d]
+    const int row0 = wg * RT;
+    float S[RT][4];
 #pragma unroll
-    for (int i = 0; i < BAND; ++i) S[i] = (row0 + i < d) ? st[(size_t)(row0 + i) * 32 + lane] : 0.0f;
-    const int col = slice * 32 + lane;
-
-    for (int c0 = r0; c0 < r1; c0 += MLSTM_CHUNK) {
-        const int nc = min(MLSTM_CHUNK, r1 - c0);
-        __syncthreads();                                 // the previous chunk's partial sums have been read
-        for (int i = threadIdx.x; i < nc * DP; i += blockDim.x) {
-            const int t = i / DP, c = i - t * DP;
-            const float* row = a.proj + (size_t)(c0 + t) * a.ld;
-            k_s[i] = c < d ? row[a.col_k + h * d + c] : 0.0f;
-            q_s[i] = c < d ? row[a.col_q + h * d + c] * a.q_scale : 0.0f;
-        }
-        for (int i = threadIdx.x; i < nc * 32; i += blockDim.x) {
-            const int t = i >> 5, c = slice * 32 + (i & 31);
-            v_s[i] = c < dv ? a.proj[(size_t)(c0 + t) * a.ld + a.col_v + h * dv + c] : 0.0f;
-        }
-        for (int i = threadIdx.x; i < nc * 4; i += blockDim.x)
-            c_s[i] = a.coef[((size_t)(c0 + (i >> 2)) * a.heads + h) * 4 + (i & 3)];
-        __syncthreads();
-        for (int t = 0; t < nc; ++t) {
-            const float ca = c_s[t * 4], bv = c_s[t * 4 + 1] * v_s[t * 32 + lane];
-            const float* kt = k_s + t * DP + row0;
-            const float* qt = q_s + t * DP + row0;
-            float part = 0.0f;
+    for (int i = 0; i < RT; ++i) {
 #pragma unroll
-            for (int i = 0; i < BAND; ++i) {
-                S[i] = fmaf(ca, S[i], kt[i] * bv);
-                part = fmaf(S[i], qt[i], part);
+        for (int j = 0; j < 4; ++j) {
+            S[i][j] = 0.0f;
+            if (row0 + i < d) {
+                if (!norm_slice) S[i][j] = st[(size_t)(row0 + i) * 32 + c4 + j];
+                else if (c4 + j == 0) S[i][j] = st[row0 + i];
             }
-            p_s[(t * MLSTM_WARPS + warp) * 32 + lane] = part;
+        }
+    }
+    auto fetch = [&](int c0, int stage) {                // the chunk that starts at row c0, on its way into a stage
+        const int nc = min(CHUNK, r1 - c0);
+#pragma unroll
+        for (int j = 0; j < PER_THREAD; ++j) {
+            const int i = tid + j * SCAN_THREADS, t = i / DP, x = i - t * DP;
+            const bool ok = t < nc && x < d;
+            const float* row = a.proj + (size_t)(c0 + (ok ? t : 0)) * a.ld + h * d + (ok ? x : 0);
+            copy_async_f32(&k_s[stage][i], row + a.col_k, ok);
+            copy_async_f32(&q_s[stage][i], row + a.col_q, ok);
+        }
+#pragma unroll
+        for (int j = 0; j < V_PER_THREAD; ++j) {
+            const int i = tid + j * SCAN_THREADS, t = i >> 5, x = i & 31;
+            if (norm_slice) {
+                v_s[stage][i] = (t < nc && x == 0) ? 1.0f : 0.0f;
+            } else {
+                const bool ok = t < nc && slice * 32 + x < dv;
+                copy_async_f32(&v_s[stage][i], a.proj + (size_t)(c0 + (ok ? t : 0)) * a.ld + a.col_v + h * dv +
+                                                   (ok ? slice * 32 + x : 0), ok);
+            }
+        }
+        if (tid < CHUNK * 2) {
+            const bool ok = (tid >> 1) < nc;
+            copy_async_f32(&c_s[stage][tid], a.coef + ((size_t)(c0 + (ok ? tid >> 1 : 0)) * a.heads + h) * 4 + (tid & 1), ok);
+        }
+        copy_async_commit();
+    };
+    fetch(r0, 0);
+    int stage = 0;
+    for (int c0 = r0; c0 < r1; c0 += CHUNK, stage ^= 1) {
+        const int nc = min(CHUNK, r1 - c0);
+        copy_async_wait_all();
+        __syncthreads();              // this chunk has arrived; the other stage and the partial sums have been read
+        if (c0 + CHUNK < r1) fetch(c0 + CHUNK, stage ^ 1);
+        for (int t = 0; t < nc; ++t) {
+            const float ca = expf(c_s[stage][t * 2]), cb = expf(c_s[stage][t * 2 + 1]);
+            const float4 v4 = *reinterpret_cast<const float4*>(&v_s[stage][t * 32 + c4]);
+            const float bv[4] = {cb * v4.x, cb * v4.y, cb * v4.z, cb * v4.w};
+            const float* kt = &k_s[stage][t * DP + row0];
+            const float* qt = &q_s[stage][t * DP + row0];
+            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int i = 0; i < RT; ++i) {
+                const float kk = kt[i], qq = qt[i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    S[i][j] = fmaf(ca, S[i][j], kk * bv[j]);
+                    part[j] = fmaf(S[i][j], qq, part[j]);
+                }
+            }
+            *reinterpret_cast<float4*>(p_s + (t * 16 + wg) * 32 + c4) = make_float4(part[0], part[1], part[2], part[3]);
         }
         __syncthreads();
-        for (int t = warp; t < nc; t += MLSTM_WARPS) {
-            float num = 0.0f;
+        for (int idx = tid; idx < nc * 32; idx += SCAN_THREADS) {
+            const int t = idx >> 5, x = idx & 31;
+            float sum = 0.0f;
 #pragma unroll
-            for (int w = 0; w < MLSTM_WARPS; ++w) num += p_s[(t * MLSTM_WARPS + w) * 32 + lane];
-            if (col < dv) a.o_raw[(size_t)(c0 + t) * a.heads * dv + h * dv + col] = num / c_s[t * 4 + 2];
+            for (int w = 0; w < 16; ++w) sum += p_s[(t * 16 + w) * 32 + x];
+            sum *= a.q_scale;                            // the query's factor, applied to the finished sum
+            if (norm_slice) {
+                if (x == 0) a.nq[(size_t)(c0 + t) * a.heads + h] = sum;
+            } else if (slice * 32 + x < dv) {
+                a.o_raw[(size_t)(c0 + t) * a.heads * dv + h * dv + slice * 32 + x] = sum;
+            }
         }
     }
 #pragma unroll
-    for (int i = 0; i < BAND; ++i)
-        if (row0 + i < d) st[(size_t)(row0 + i) * 32 + lane] = S[i];
+    for (int i = 0; i < RT; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (row0 + i < d) {
+                if (!norm_slice) st[(size_t)(row0 + i) * 32 + c4 + j] = S[i][j];
+                else if (c4 + j == 0) st[row0 + i] = S[i][j];
+            }
+        }
+    }
 }
 
-static size_t scan_smem_bytes(int band) {
-    const int dp = band * MLSTM_WARPS;
-    return sizeof(float) * (size_t)(2 * MLSTM_CHUNK * dp + MLSTM_CHUNK * 32 + MLSTM_CHUNK * 4 +
-                                    MLSTM_CHUNK * MLSTM_WARPS * 32);
-}
-
-template <int BAND>
+template <int RT>
 static int launch_scan(const MlstmArgs& a, int B, cudaStream_t stream) {
-    const size_t smem = scan_smem_bytes(BAND);
-    auto kern = mlstm_scan_kernel<BAND>;
-    if (smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return SHARPI_LAUNCH_FAILED;
-    kern<<<dim3(B, a.heads, a.slices), MLSTM_WARPS * 32, smem, stream>>>(a);
+    mlstm_scan_kernel<RT><<<dim3(B, a.heads, a.slices + 1), SCAN_THREADS, 0, stream>>>(a);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
 
-// The recurrence over the step's rows: leaves o_raw [T, heads * dv] (before the head norm) and the new state.
-// `coef` is scratch of T * heads * 4 floats.
+// The recurrence over the step's rows: leaves the numerators o_raw [T, heads * dv], n . q in nq [T, heads], the
+// running maximum of every row in coef[.., 2] (coef: T * heads * 4 floats) and the new state.
 SHARPI_API int sharpi_mlstm_recurrence(const float* proj, int ld, int col_q, int col_k, int col_v, int col_i, int col_f,
                                        const float* bias_i, const float* bias_f, const int* row_offsets,
                                        const int* state_slots, float* state, long long state_stride, int head_stride,
                                        int B, int T, int heads, int d, int dv, float cap, float q_scale, float* coef,
-                                       float* o_raw, cudaStream_t stream) {
+                                       float* o_raw, float* nq, cudaStream_t stream) {
     if (B <= 0 || T <= 0) return SHARPI_OK;
     if (heads <= 0 || d <= 0 || dv <= 0 || d > MLSTM_MAX_D || !(cap > 0.0f)) return SHARPI_BAD_ARGUMENT;
-    if (heads > 65535 || (dv + 31) / 32 > 65535) return SHARPI_BAD_ARGUMENT;
+    if (heads > 65535 || (dv + 31) / 32 + 1 > 65535) return SHARPI_BAD_ARGUMENT;
     MlstmArgs a;
-    a.proj = proj; a.ld = ld; a.col_q = col_q; a.col_k = col_k; a.col_v = col_v; a.col_g = 0; a.col_i = col_i;
+    a.proj = proj; a.ld = ld; a.col_q = col_q; a.col_k = col_k; a.col_v = col_v; a.col_i = col_i;
     a.col_f = col_f; a.bias_i = bias_i; a.bias_f = bias_f; a.row_offsets = row_offsets; a.state_slots = state_slots;
     a.state = state; a.state_stride = state_stride; a.head_stride = head_stride; a.heads = heads; a.d = d; a.dv = dv;
-    a.slices = (dv + 31) / 32; a.cap = cap; a.q_scale = q_scale; a.coef = coef; a.o_raw = o_raw;
+    a.slices = (dv + 31) / 32; a.cap = cap; a.q_scale = q_scale; a.coef = coef; a.o_raw = o_raw; a.nq = nq;
     if ((long long)head_stride < (long long)a.slices * d * 32 + d + 1) return SHARPI_BAD_ARGUMENT;
-    const dim3 grid(B, heads);
-    if (d <= 32) mlstm_gates_kernel<1><<<grid, 32, 0, stream>>>(a);
-    else if (d <= 64) mlstm_gates_kernel<2><<<grid, 32, 0, stream>>>(a);
-    else if (d <= 128) mlstm_gates_kernel<4><<<grid, 32, 0, stream>>>(a);
-    else mlstm_gates_kernel<8><<<grid, 32, 0, stream>>>(a);
+    mlstm_gates_kernel<<<dim3(B, heads), 32, 0, stream>>>(a);
     SHARPI_CHECK_LAUNCH();
-    if (d <= 16) return launch_scan<2>(a, B, stream);
-    if (d <= 32) return launch_scan<4>(a, B, stream);
-    if (d <= 64) return launch_scan<8>(a, B, stream);
-    if (d <= 128) return launch_scan<16>(a, B, stream);
-    return launch_scan<32>(a, B, stream);
+    if (d <= 16) return launch_scan<1>(a, B, stream);
+    if (d <= 32) return launch_scan<2>(a, B, stream);
+    if (d <= 64) return launch_scan<4>(a, B, stream);
+    if (d <= 128) return launch_scan<8>(a, B, stream);
+    return launch_scan<16>(a, B, stream);
 }
 
 // ---------------------------------------------------------------------------------------
+// o[t, h, :] = num[t, h, :] / (max(|nq[t, h]|, exp(-m[t, h])) + 1e-6)
 // out[t, h, :] = o[t, h, :] * rsqrt(mean(o[t, h, :]^2) + eps) * w[h, :] * sigmoid(gate[t, h, :])
 // One warp per (row, head).
 // ---------------------------------------------------------------------------------------
 template <typename TO>
-__global__ void mlstm_out_kernel(const float* __restrict__ o_raw, const float* __restrict__ gate, int gate_ld,
+__global__ void mlstm_out_kernel(const float* __restrict__ o_raw, const float* __restrict__ nq,
+                                 const float* __restrict__ coef, const float* __restrict__ gate, int gate_ld,
                                  const float* __restrict__ w, float eps, long long work, int heads, int dv,
                                  TO* __restrict__ out) {
     const int lane = threadIdx.x & 31;
@@ -247,18 +277,22 @@ __global__ void mlstm_out_kernel(const float* __restrict__ o_raw, const float* _
     const int h = (int)(item - t * heads);
     const float* o = o_raw + (size_t)t * heads * dv + (size_t)h * dv;
     const float* g = gate + (size_t)t * gate_ld + (size_t)h * dv;
+    const float den = fmaxf(fabsf(nq[item]), expf(-coef[item * 4 + 2])) + 1e-6f;
     float ss = 0.0f;
-    for (int c = lane; c < dv; c += 32) ss = fmaf(o[c], o[c], ss);
+    for (int c = lane; c < dv; c += 32) {
+        const float v = o[c] / den;
+        ss = fmaf(v, v, ss);
+    }
     ss = warp_sum(ss);
     const float scale = 1.0f / sqrtf(ss / (float)dv + eps);
     TO* dst = out + (size_t)t * heads * dv + (size_t)h * dv;
     for (int c = lane; c < dv; c += 32) {
         const float s = 1.0f / (1.0f + expf(-g[c]));
-        dst[c] = from_float<TO>(o[c] * scale * w[h * dv + c] * s);
+        dst[c] = from_float<TO>(o[c] / den * scale * w[h * dv + c] * s);
     }
 }
 
-SHARPI_API int sharpi_mlstm_out(const float* o_raw, const float* gate, int gate_ld, const float* w, float eps, int T,
+SHARPI_API int sharpi_mlstm_out(const float* o_raw, const float* nq, const float* coef, const float* gate, int gate_ld, const float* w, float eps, int T,
                                 int heads, int dv, void* out, int out_dtype, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (heads <= 0 || dv <= 0) return SHARPI_BAD_ARGUMENT;
@@ -267,9 +301,9 @@ SHARPI_API int sharpi_mlstm_out(const float* o_raw, const float* gate, int gate_
     const long long blocks = (work + warps - 1) / warps;
     if (blocks > 2147483647LL) return SHARPI_BAD_ARGUMENT;
     if (out_dtype == SHARPI_F32)
-        mlstm_out_kernel<float><<<(unsigned)blocks, warps * 32, 0, stream>>>(o_raw, gate, gate_ld, w, eps, work, heads, dv, (float*)out);
+        mlstm_out_kernel<float><<<(unsigned)blocks, warps * 32, 0, stream>>>(o_raw, nq, coef, gate, gate_ld, w, eps, work, heads, dv, (float*)out);
     else if (out_dtype == SHARPI_BF16)
-        mlstm_out_kernel<bf16><<<(unsigned)blocks, warps * 32, 0, stream>>>(o_raw, gate, gate_ld, w, eps, work, heads, dv, (bf16*)out);
+        mlstm_out_kernel<bf16><<<(unsigned)blocks, warps * 32, 0, stream>>>(o_raw, nq, coef, gate, gate_ld, w, eps, work, heads, dv, (bf16*)out);
     else
         return SHARPI_BAD_ARGUMENT;
     SHARPI_CHECK_LAUNCH();

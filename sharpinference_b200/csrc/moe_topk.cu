@@ -2,7 +2,7 @@
 //
 //   router_topk   z = h Wr^T (float32), s = sigmoid(z); the k experts with the largest s + correction (the lowest
 //                 index among equals) are chosen; each weight is scale * s (without the correction), divided by the
-//                 sum of the chosen s first when `renormalize`.  One warp per row: a row's logits are one fixed
+//                 sum of the chosen s first when `renormalize`.  One CTA per row: a row's logits are one fixed
 //                 sequence of additions whatever else the step holds.
 //   pair_tokens   after the (row, choice) pairs have been sorted by expert: the row each sorted pair belongs to.
 //   combine       out[t] = add[t] + sum over the row's k pairs of y[pair], in the order of the choices.
@@ -11,32 +11,40 @@
 // routing stays on the device so that a step's rows can be sorted by expert for grouped products.
 #include "common.cuh"
 
-constexpr int TOPK_WARPS = 4;
+constexpr int TOPK_WARPS = 8;
 
+// One CTA per row: warp w forms the logits of experts w, w + 8, ... (a lane adds its elements of the row in
+// ascending order in four interleaved chains, the chains and then the lanes are added in a fixed order), then
+// warp 0 picks the k best.
 __global__ void __launch_bounds__(TOPK_WARPS * 32)
 router_topk_kernel(const float* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ correction,
-                   int T, int H, int E, int k, float scale, int renormalize, int* __restrict__ expert_id,
+                   int H, int E, int k, float scale, int renormalize, int* __restrict__ expert_id,
                    float* __restrict__ weight, float* __restrict__ scores_out) {
-    extern __shared__ float smem[];                       // per warp: s [E], choice [E]
+    extern __shared__ float smem[];                       // s [E], choice [E]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * TOPK_WARPS + warp;
-    if (t >= T) return;
-    float* s_s = smem + (size_t)warp * 2 * E;
+    const int t = blockIdx.x;
+    float* s_s = smem;
     float* c_s = s_s + E;
     const float* row = h + (size_t)t * H;
-    for (int e = 0; e < E; ++e) {
+    for (int e = warp; e < E; e += TOPK_WARPS) {
         const float* w = wr + (size_t)e * H;
-        float acc = 0.0f;
-        for (int i = lane; i < H; i += 32) acc = fmaf(row[i], w[i], acc);
-        acc = warp_sum(acc);
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        int i = lane;
+        for (; i + 96 < H; i += 128) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] = fmaf(row[i + 32 * u], w[i + 32 * u], acc[u]);
+        }
+        for (int u = 0; i < H; i += 32, ++u) acc[u] = fmaf(row[i], w[i], acc[u]);
+        const float z = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
         if (lane == 0) {
-            const float s = 1.0f / (1.0f + expf(-acc));
+            const float s = 1.0f / (1.0f + expf(-z));
             s_s[e] = s;
             c_s[e] = correction ? s + correction[e] : s;
             if (scores_out) scores_out[(size_t)t * E + e] = s;
         }
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     float total = 0.0f;
     int mine = 0;                                          // lane j keeps the j-th choice
     for (int j = 0; j < k; ++j) {
@@ -70,10 +78,10 @@ SHARPI_API int sharpi_router_topk(const float* h, const float* wr, const float* 
                                   cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (H <= 0 || E <= 0 || k <= 0 || k > E || k > 32) return SHARPI_BAD_ARGUMENT;
-    const size_t smem = (size_t)TOPK_WARPS * 2 * E * sizeof(float);
+    const size_t smem = (size_t)2 * E * sizeof(float);
     if (smem > 48 * 1024) return SHARPI_BAD_ARGUMENT;
-    router_topk_kernel<<<(T + TOPK_WARPS - 1) / TOPK_WARPS, TOPK_WARPS * 32, smem, stream>>>(
-        h, wr, correction, T, H, E, k, scale, renormalize, expert_id, weight, scores_out);
+    router_topk_kernel<<<T, TOPK_WARPS * 32, smem, stream>>>(h, wr, correction, H, E, k, scale, renormalize, expert_id,
+                                                              weight, scores_out);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }

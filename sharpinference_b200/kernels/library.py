@@ -56,8 +56,8 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_router_topk": ("moe_topk", [P, P, P, I, I, I, I, F, I, P, P, P, P]),
     "sharpi_moe_pair_tokens": ("moe_topk", [P, I, I, P, P]),
     "sharpi_moe_combine": ("moe_topk", [P, P, P, I, I, I, P]),
-    "sharpi_mlstm_recurrence": ("mlstm", [P, I, I, I, I, I, I, P, P, P, P, P, LL, I, I, I, I, I, I, F, F, P, P, P]),
-    "sharpi_mlstm_out": ("mlstm", [P, P, I, P, F, I, I, I, P, I, P]),
+    "sharpi_mlstm_recurrence": ("mlstm", [P, I, I, I, I, I, I, P, P, P, P, P, LL, I, I, I, I, I, I, F, F, P, P, P, P]),
+    "sharpi_mlstm_out": ("mlstm", [P, P, P, P, I, P, F, I, I, I, P, I, P]),
 }
 
 _libs: Dict[str, ctypes.CDLL] = {}

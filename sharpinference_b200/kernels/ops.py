@@ -694,8 +694,9 @@ MLSTM_MAX_KEY_SIZE = 256
 
 
 def mlstm_state_floats(heads: int, d: int, dv: int):
-    """``(floats per head, floats per request)`` of the matrix-memory state: per head the value columns in slices of
-    32 ``[slices, d, 32]``, then the normaliser ``[d]``, then the running maximum (padded to four floats)."""
+    """``(floats per head, floats per request)`` of the matrix-memory state: per head, for every slice of 32 value
+    columns ``[d, 32]`` of the memory, then the normaliser ``[d]``, then the running maximum (padded to four
+    floats)."""
     slices = (dv + 31) // 32
     per_head = slices * d * 32 + d + 4
     return per_head, heads * per_head
@@ -703,11 +704,12 @@ def mlstm_state_floats(heads: int, d: int, dv: int):
 
 def mlstm_recurrence(proj: torch.Tensor, *, col_q: int, col_k: int, col_v: int, col_i: int, col_f: int,
                      bias_i: torch.Tensor, bias_f: torch.Tensor, row_offsets: torch.Tensor, state_slots: torch.Tensor,
-                     state: torch.Tensor, heads: int, d: int, dv: int, cap: float, q_scale: float) -> torch.Tensor:
+                     state: torch.Tensor, heads: int, d: int, dv: int, cap: float, q_scale: float):
     """The matrix-memory recurrence over the step's rows (``mlstm.cu``): reads q, k, v and the raw gates from the
-    fused float32 projection ``proj [T, ld]`` at the given first columns, advances ``state [slots, floats]`` of
-    the step's requests (``state_slots [B]``, rows ``row_offsets [B + 1]``) and returns the unnormalised head
-    outputs, float32 ``[T, heads * dv]``."""
+    fused float32 projection ``proj [T, ld]`` at the given first columns and advances ``state [slots, floats]`` of
+    the step's requests (``state_slots [B]``, rows ``row_offsets [B + 1]``).  Returns ``(num, nq, coef)``: the
+    numerators ``S^T q`` float32 ``[T, heads * dv]``, ``n . q`` ``[T, heads]`` and per row and head ``(log a, log b,
+    m, -)``, which :func:`mlstm_out` turns into the mixer's output."""
     _need(proj, "proj", torch.float32)
     _need(bias_i, "bias_i", torch.float32)
     _need(bias_f, "bias_f", torch.float32)
@@ -725,18 +727,25 @@ def mlstm_recurrence(proj: torch.Tensor, *, col_q: int, col_k: int, col_v: int, 
         raise KernelError("a part of the fused projection lies outside its columns")
     coef = torch.empty((T, heads, 4), dtype=torch.float32, device=proj.device)
     o_raw = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
+    nq = torch.empty((T, heads), dtype=torch.float32, device=proj.device)
     check(kernel("sharpi_mlstm_recurrence")(proj.data_ptr(), ld, col_q, col_k, col_v, col_i, col_f, bias_i.data_ptr(),
                                             bias_f.data_ptr(), row_offsets.data_ptr(), state_slots.data_ptr(),
                                             state.data_ptr(), state.stride(0), per_head, B, T, heads, d, dv,
-                                            float(cap), float(q_scale), coef.data_ptr(), o_raw.data_ptr(), _stream()),
+                                            float(cap), float(q_scale), coef.data_ptr(), o_raw.data_ptr(), nq.data_ptr(),
+                                            _stream()),
           "sharpi_mlstm_recurrence")
-    return o_raw
+    return o_raw, nq, coef
 
 
-def mlstm_out(o_raw: torch.Tensor, proj: torch.Tensor, col_g: int, weight: torch.Tensor, eps: float, heads: int,
-              dv: int, out_dtype: torch.dtype) -> torch.Tensor:
-    """Per head: ``o / rms(o) * weight * sigmoid(gate)`` with the gate read from ``proj[:, col_g:]``."""
+def mlstm_out(o_raw: torch.Tensor, nq: torch.Tensor, coef: torch.Tensor, proj: torch.Tensor, col_g: int,
+              weight: torch.Tensor, eps: float, heads: int, dv: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per row and head: ``o = num / (max(|n . q|, exp(-m)) + 1e-6)``, then ``o / rms(o) * weight * sigmoid(gate)``
+    with the gate read from ``proj[:, col_g:]``."""
     _need(o_raw, "o_raw", torch.float32)
+    _need(nq, "nq", torch.float32)
+    _need(coef, "coef", torch.float32)
+    if nq.numel() != o_raw.shape[0] * heads or coef.numel() != 4 * nq.numel():
+        raise KernelError("n . q and the coefficients must hold one entry (four) per row and head")
     _need(proj, "proj", torch.float32)
     _need(weight, "weight", torch.float32)
     T = o_raw.shape[0]
@@ -744,7 +753,7 @@ def mlstm_out(o_raw: torch.Tensor, proj: torch.Tensor, col_g: int, weight: torch
         raise KernelError("head outputs, gate columns and norm weight disagree on heads * value size")
     out = torch.empty((T, heads * dv), dtype=out_dtype, device=o_raw.device)
     gate = proj[:, col_g:]
-    check(kernel("sharpi_mlstm_out")(o_raw.data_ptr(), gate.data_ptr(), proj.shape[1], weight.data_ptr(), float(eps), T,
+    check(kernel("sharpi_mlstm_out")(o_raw.data_ptr(), nq.data_ptr(), coef.data_ptr(), gate.data_ptr(), proj.shape[1], weight.data_ptr(), float(eps), T,
                                      heads, dv, out.data_ptr(), dtype_code(out_dtype), _stream()), "sharpi_mlstm_out")
     return out
 

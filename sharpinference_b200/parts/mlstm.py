@@ -24,8 +24,6 @@ The reference keeps per-sequence state of fixed size for another recurrent layer
 """
 from __future__ import annotations
 
-from typing import Optional
-
 import torch
 
 from ..kernels import ops
@@ -78,11 +76,11 @@ class MLSTMMixer(Mixer):
 
     def forward(self, ctx: StepContext, slot: LayerSlot, h: torch.Tensor) -> torch.Tensor:
         p = self.proj(h)                                                    # [T, fused] float32
-        o_raw = ops.mlstm_recurrence(p, col_q=self.col_q, col_k=self.col_k, col_v=self.col_v, col_i=self.col_i,
-                                     col_f=self.col_f, bias_i=self.bias_i, bias_f=self.bias_f,
-                                     row_offsets=ctx.row_offsets, state_slots=ctx.state_slots, state=slot.state,
-                                     heads=self.heads, d=self.key_dim, dv=self.value_dim, cap=self.gate_cap,
-                                     q_scale=self.q_scale)
-        o = ops.mlstm_out(o_raw, p, self.col_g, self.head_norm_weight, self.eps, self.heads, self.value_dim,
+        num, nq, coef = ops.mlstm_recurrence(
+            p, col_q=self.col_q, col_k=self.col_k, col_v=self.col_v, col_i=self.col_i, col_f=self.col_f,
+            bias_i=self.bias_i, bias_f=self.bias_f, row_offsets=ctx.row_offsets, state_slots=ctx.state_slots,
+            state=slot.state, heads=self.heads, d=self.key_dim, dv=self.value_dim, cap=self.gate_cap,
+            q_scale=self.q_scale)
+        o = ops.mlstm_out(num, nq, coef, p, self.col_g, self.head_norm_weight, self.eps, self.heads, self.value_dim,
                           self.act_dtype)
         return self.out(o)

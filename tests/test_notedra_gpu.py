@@ -184,10 +184,12 @@ def test_mlstm_recurrence_kernel(heads, d, dv):
         offs = [0]
         for b in live:
             offs.append(offs[-1] + lens[b][step])
-        o = ops.mlstm_recurrence(rows, col_q=cq, col_k=ck, col_v=cv, col_i=ci, col_f=cf, bias_i=bias_i.to(DEV),
+        num, nq, coef = ops.mlstm_recurrence(rows, col_q=cq, col_k=ck, col_v=cv, col_i=ci, col_f=cf, bias_i=bias_i.to(DEV),
                                  bias_f=bias_f.to(DEV), row_offsets=torch.tensor(offs, dtype=torch.int32, device=DEV),
                                  state_slots=torch.tensor([slots[b] for b in live], dtype=torch.int32, device=DEV),
                                  state=state, heads=heads, d=d, dv=dv, cap=cap, q_scale=d ** -0.5)
+        den = torch.maximum(nq.abs(), torch.exp(-coef[:, :, 2])) + 1e-6
+        o = (num.view(-1, heads, dv) / den[:, :, None]).reshape(-1, heads * dv)
         for j, b in enumerate(live):
             got[b].append(o[offs[j]:offs[j + 1]].double().cpu())
     assert torch.all(state[2] == 7.0) and torch.all(state[4] == 0.0)
@@ -202,13 +204,14 @@ def test_mlstm_recurrence_kernel(heads, d, dv):
                 st, want[t, hd] = plain.mlstm_step(st, p[t, cq + hd * d:cq + (hd + 1) * d] * d ** -0.5,
                                                    p[t, ck + hd * d:ck + (hd + 1) * d],
                                                    p[t, cv + hd * dv:cv + (hd + 1) * dv], ig[t, hd], fg[t, hd])
-            # the state that the kernels left: S in slices of 32 value columns, then n, then m
+            # the state that the kernels left: slices of 32 value columns [d, 32], then n [d], then m
             S, n, m = st
             flat = state[slots[b]].double().cpu()[hd * per_head:(hd + 1) * per_head]
             slices = (dv + 31) // 32
-            S_got = flat[:slices * d * 32].view(slices, d, 32).permute(1, 0, 2).reshape(d, slices * 32)[:, :dv]
+            S_got = flat[:slices * d * 32].view(slices, d, 32).permute(1, 0, 2).reshape(d, slices * 32)
             scale = max(1.0, float(S.abs().max()))
-            assert torch.allclose(S_got, S, atol=2e-5 * scale), (b, hd)
+            assert torch.allclose(S_got[:, :dv], S, atol=2e-5 * scale), (b, hd)
+            assert torch.all(S_got[:, dv:] == 0)
             assert torch.allclose(flat[slices * d * 32:slices * d * 32 + d], n, atol=2e-5 * max(1.0, float(n.abs().max())))
             assert flat[slices * d * 32 + d].item() == pytest.approx(float(m), abs=1e-5)
         have = torch.cat(got[b]).view(total[b], heads, dv)
@@ -219,11 +222,16 @@ def test_mlstm_out_kernel():
     from sharpinference_b200.kernels import ops
     g = torch.Generator().manual_seed(9)
     T, heads, dv, col_g, ld = 13, 3, 40, 17, 17 + 120 + 5
-    o = torch.randn(T, heads * dv, generator=g) * 4
+    num = torch.randn(T, heads * dv, generator=g) * 4
+    nq = torch.randn(T, heads, generator=g) * 2          # some below exp(-m) in size, some above
+    coef = torch.randn(T, heads, 4, generator=g)
     proj = torch.randn(T, ld, generator=g)
     w = torch.randn(heads * dv, generator=g)
-    got = ops.mlstm_out(o.to(DEV), proj.to(DEV), col_g, w.to(DEV), 1e-4, heads, dv, torch.float32)
-    want = plain.unit_rms(o.double().view(T, heads, dv), 1e-4).reshape(T, -1) * w.double() \
+    got = ops.mlstm_out(num.to(DEV), nq.to(DEV), coef.to(DEV), proj.to(DEV), col_g, w.to(DEV), 1e-4, heads, dv,
+                        torch.float32)
+    den = torch.maximum(nq.double().abs(), torch.exp(-coef.double()[:, :, 2])) + 1e-6
+    o = num.double().view(T, heads, dv) / den[:, :, None]
+    want = plain.unit_rms(o, 1e-4).reshape(T, -1) * w.double() \
         * torch.sigmoid(proj.double()[:, col_g:col_g + heads * dv])
     assert torch.allclose(got.double().cpu(), want, atol=1e-5)
 
