@@ -154,9 +154,9 @@ def main(argv=None) -> int:
             for layer, norms in enumerate(engine.runner.last_layer_norms):
                 block = engine.model.blocks[engine.model.schedule[layer].layer]
                 routed = getattr(getattr(block, "ffn", None), "num_experts", 0) > 0
-                expert = int(next(picks)[-1]) if routed else None
+                expert = next(picks)[-1].reshape(-1).tolist() if routed else None      # one expert a row, or several
                 print(f"step {steps} layer {layer}: |x| = {float(norms[-1]):.6f}"
-                      + (f", expert {expert}" if expert is not None else ""), file=sys.stderr)
+                      + (f", expert {' '.join(map(str, expert))}" if expert is not None else ""), file=sys.stderr)
         steps += 1
         if t_first is None and all(engine.output(i).tokens or engine.output(i).finished for i in ids):
             torch.cuda.synchronize()

@@ -50,6 +50,8 @@ struct TcGemmParams {
     int* status;                // device word: 0 ok, else the code of the wait that gave up
     int rows, N, K, E;          // N: weight rows per expert (MODE_SWIGLU: 2 I)
     int accumulate;
+    int store_act;              // MODE_STORE: 0 = float32 out as above; 1 / 2 / 3 = bf16 out [rows, N] (sorted rows) of
+                                // relu(x)^2 / tanh-GELU(x) / SiLU(x): the first product of a two-layer expert
     // K split over gridDim.z CTAs (few rows and few experts: not enough tiles to fill the GPU otherwise).
     // Each CTA then leaves its raw fp32 accumulators in partial[z][sorted row][N]; the one that finishes last
     // adds the parts in the order of z and applies the epilogue.
@@ -92,6 +94,12 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return g * rcp_approx(1.0f + ex2_approx(-1.4426950408889634f * g)) * u;
 }
 
+__device__ __forceinline__ float store_activation(int kind, float x) {
+    if (kind == 1) { const float r = fmaxf(x, 0.0f); return r * r; }
+    if (kind == 2) return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return x / (1.0f + expf(-x));
+}
+
 // The epilogue of 16 accumulator columns (sorted rows r_first .. r_first + 15, of which `count` exist) of one
 // thread's weight row(s): g from the first weight tile (row n), u from the second (MODE_SWIGLU: the matching
 // up row; MODE_STORE: row n + 128, if the CTA has a second tile).
@@ -124,6 +132,19 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const f
         float* C = reinterpret_cast<float*>(p.out);
         const bool n_ok = n < p.N, nb_ok = two_tiles && n + TC_BM < p.N;
         const bool scaled = p.row_scale != nullptr;      // a router that weights the experts' outputs
+        if (p.store_act) {                               // activation in the epilogue, bf16 rows in sorted order
+            bf16* A = reinterpret_cast<bf16*>(p.out);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (j < count) {
+                    bf16* dst = A + (size_t)(r_first + j) * p.N + n;
+                    const float gv = scaled ? g[j] * sc[j] : g[j], uv = scaled ? u[j] * sc[j] : u[j];
+                    if (n_ok) *dst = __float2bfloat16_rn(store_activation(p.store_act, gv));
+                    if (nb_ok) dst[TC_BM] = __float2bfloat16_rn(store_activation(p.store_act, uv));
+                }
+            }
+            return;
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             if (j < count) {
@@ -710,11 +731,14 @@ SHARPI_API void sharpi_tc_set_wait_test(unsigned limit, int drop_from) {
 // persistent kernel (up to 256 groups, no K split), which `max_ctas` > 0 keeps to that many SMs.
 // `k_split` > 1 (with `partial`, k_split * rows * N floats of scratch, and `tickets`, one zero int per tile of the
 // launch grid) cuts K over that many CTAs per tile.
-SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* group_offsets, void* out,
-                                      const int* out_rows, const float* row_scale, const int* scale_rows,
-                                      int* status, float* partial, int* tickets, int rows, int N, int K, int E, int mode,
-                                      int row_tile, int accumulate, int k_split, int max_ctas, cudaStream_t stream) {
+static int tc_grouped_gemm_impl(const void* A, const void* W, const int* group_offsets, void* out,
+                               const int* out_rows, const float* row_scale, const int* scale_rows,
+                               int* status, float* partial, int* tickets, int rows, int N, int K, int E, int mode,
+                               int row_tile, int accumulate, int k_split, int max_ctas, int store_act,
+                               cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return SHARPI_OK;
+    if (store_act < 0 || store_act > 3 || (store_act && (mode != MODE_STORE || accumulate || out_rows)))
+        return SHARPI_BAD_ARGUMENT;
     if (K <= 0 || E <= 0 || K % 8 != 0) return SHARPI_BAD_ARGUMENT;          // TMA: rows 16-byte aligned
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return SHARPI_UNALIGNED;
     if (mode == MODE_SWIGLU && (N % 2 != 0)) return SHARPI_BAD_ARGUMENT;
@@ -726,6 +750,7 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
     TcGemmParams p;
     p.group_offsets = group_offsets; p.out_rows = out_rows; p.row_scale = row_scale; p.scale_rows = scale_rows;
     p.out = out; p.status = status; p.rows = rows; p.N = N; p.K = K; p.E = E; p.accumulate = accumulate;
+    p.store_act = store_act;
     if (k_split < 1 || k_split > 16 || (k_split > 1 && (!partial || !tickets))) return SHARPI_BAD_ARGUMENT;
     p.partial = partial; p.k_split = k_split; p.tickets = tickets;
     p.wait_limit = g_test_wait_limit ? g_test_wait_limit : WAIT_LIMIT;
@@ -762,6 +787,24 @@ SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* g
     TC_CASE(MODE_SWIGLU, 256, 2)
 #undef TC_CASE
     return rc;
+}
+
+SHARPI_API int sharpi_tc_grouped_gemm(const void* A, const void* W, const int* group_offsets, void* out,
+                                      const int* out_rows, const float* row_scale, const int* scale_rows,
+                                      int* status, float* partial, int* tickets, int rows, int N, int K, int E, int mode,
+                                      int row_tile, int accumulate, int k_split, int max_ctas, cudaStream_t stream) {
+    return tc_grouped_gemm_impl(A, W, group_offsets, out, out_rows, row_scale, scale_rows, status, partial, tickets, rows,
+                                N, K, E, mode, row_tile, accumulate, k_split, max_ctas, 0, stream);
+}
+
+// The store mode with an activation in the epilogue: bf16 out[r, n] = act(a[r] . w[e(r)][n]) in sorted row order
+// (act: 1 = relu^2, 2 = tanh-GELU, 3 = SiLU).
+SHARPI_API int sharpi_tc_grouped_gemm_act(const void* A, const void* W, const int* group_offsets, void* out,
+                                          int* status, float* partial, int* tickets, int rows, int N, int K, int E,
+                                          int row_tile, int k_split, int act, cudaStream_t stream) {
+    if (act < 1 || act > 3) return SHARPI_BAD_ARGUMENT;
+    return tc_grouped_gemm_impl(A, W, group_offsets, out, nullptr, nullptr, nullptr, status, partial, tickets, rows, N, K,
+                                E, MODE_STORE, row_tile, 0, k_split, 0, act, stream);
 }
 
 // out[r, :] = in[rows[r], :] for bf16 rows of width K (a multiple of 8): the activations sorted by

@@ -511,6 +511,41 @@ def tc_grouped_gemm(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tenso
     return out
 
 
+_TC_STORE_ACT = {ACT_RELU2: 1, ACT_GELU_TANH: 2, ACT_SILU: 3}
+
+
+def tc_grouped_gemm_act(a: torch.Tensor, w: torch.Tensor, group_offsets: torch.Tensor, act: int,
+                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The first product of two-layer experts on the tensor cores with the activation in the epilogue:
+    bfloat16 ``out[r] = act(a[r] . w[e(r)]^T)``, ``[rows, N]`` in sorted row order (``act``: ``ACT_RELU2``,
+    ``ACT_GELU_TANH`` or ``ACT_SILU``).  Operands as in :func:`tc_grouped_gemm`."""
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    _need(group_offsets, "group_offsets", torch.int32)
+    rows, K = a.shape
+    E, N, Kw = w.shape
+    if Kw != K or group_offsets.numel() != E + 1:
+        raise KernelError(f"shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, offsets {group_offsets.numel()}")
+    if K % 8 != 0:
+        raise KernelError(f"the tensor-core product needs an inner size that is a multiple of 8, found {K}")
+    if act not in _TC_STORE_ACT:
+        raise KernelError(f"unknown activation code {act}")
+    if out is None:
+        out = torch.empty((rows, N), dtype=torch.bfloat16, device=a.device)
+    _need(out, "out", torch.bfloat16)
+    k_split = tc_k_split(rows, N, sm_count(a.device))
+    partial = torch.empty((k_split, rows, N), dtype=torch.float32, device=a.device) if k_split > 1 else None
+    row_tile = tc_row_tile(rows, TC_MODE_STORE, E)
+    tickets = None
+    if k_split > 1:
+        tickets = zeroed_tickets(a.device, ((N + 127) // 128) * (rows // max(row_tile, 1) + min(rows, E)))
+    check(kernel("sharpi_tc_grouped_gemm_act")(a.data_ptr(), w.data_ptr(), group_offsets.data_ptr(), out.data_ptr(),
+                                               status_word(a.device).data_ptr(), _ptr(partial), _ptr(tickets), rows, N,
+                                               K, E, row_tile, k_split, _TC_STORE_ACT[act], _stream()),
+          "sharpi_tc_grouped_gemm_act")
+    return out
+
+
 def tc_set_wait_test(limit: int, drop_from: int) -> None:
     """Test hook: the next ``tc_grouped_gemm`` launch (tiled kernel) polls each wait at most ``limit`` times and
     loads nothing from K block ``drop_from`` on, so a wait runs out, the kernel records its code in the status

@@ -192,8 +192,8 @@ class MoESigmoidTopK(FeedForward):
     ``s + correction`` are chosen (``correction`` may be None; the lowest index wins among equals); an expert's
     output is weighted by ``route_scale * s`` (without the correction), the chosen ``s`` divided by their sum
     first when ``renormalize``.  The (row, choice) pairs are sorted by expert on the device; each expert multiplies
-    its rows in one grouped product (tcgen05 for bfloat16 weights whose inner sizes are multiples of 8, CUDA cores
-    otherwise), the second product scales each pair's row by its weight, and the pairs of a row are added in the
+    its rows in one grouped product (tcgen05 for bfloat16 weights whose inner sizes are multiples of 8, with the
+    activation in the first product's epilogue; CUDA cores otherwise), the second product scales each pair's row by its weight, and the pairs of a row are added in the
     order of the choices, so a row's result does not depend on the rest of the step.
 
     The reference's mixture (src/SharpInference.Engine/ForwardPass.cs:2021-2098) is top-1 with a shared expert.
@@ -241,8 +241,7 @@ class MoESigmoidTopK(FeedForward):
         y = torch.empty((T * k, self.experts_down.out_features), dtype=torch.float32, device=h.device)
         if self._tensor_core and h.dtype == torch.bfloat16:
             h_sorted = ops.gather_rows_bf16(h, pair_rows)
-            up = ops.tc_grouped_gemm(h_sorted, self.experts_up.weight, offsets, mode=ops.TC_MODE_STORE)
-            act = ops.bias_act(up, None, act_code, torch.bfloat16)
+            act = ops.tc_grouped_gemm_act(h_sorted, self.experts_up.weight, offsets, act_code)   # activation in the epilogue
             ops.tc_grouped_gemm(act, self.experts_down.weight, offsets, mode=ops.TC_MODE_STORE, out=y,
                                 out_rows=sorted_pairs, row_scale=weight.view(-1), scale_rows=sorted_pairs)
         else:

@@ -99,6 +99,27 @@ def test_bias_act(act):
     assert torch.allclose(got16.double().cpu(), want0, rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("rows,E,N,K", [(5, 3, 24, 64), (300, 4, 136, 72), (2100, 6, 96, 192)])
+def test_grouped_product_with_activation_in_the_epilogue(rows, E, N, K):
+    """The tensor-core grouped product that stores act(a . w^T) in bfloat16, against float32 arithmetic on the same
+    bfloat16 operands; few rows (K split over CTAs), a few hundred, and a few thousand."""
+    from sharpinference_b200.kernels import ops
+    g = torch.Generator().manual_seed(rows)
+    a = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, N, K, generator=g) * 0.2).to(torch.bfloat16)
+    counts = torch.multinomial(torch.ones(E), rows, replacement=True, generator=g).bincount(minlength=E)
+    offsets = torch.cat([torch.zeros(1, dtype=torch.int64), counts.cumsum(0)]).to(torch.int32)
+    for act, fn in (("relu2", plain.relu_squared), ("gelu_tanh", plain.gelu_tanh)):
+        got = ops.tc_grouped_gemm_act(a.to(DEV), w.to(DEV), offsets.to(DEV), ops.ACTIVATIONS[act])
+        ops.check_status(DEV)
+        want = torch.empty(rows, N, dtype=torch.float64)
+        for e in range(E):
+            lo, hi = int(offsets[e]), int(offsets[e + 1])
+            want[lo:hi] = fn(a[lo:hi].double() @ w[e].double().T)
+        assert got.dtype == torch.bfloat16
+        assert torch.allclose(got.double().cpu(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()))
+
+
 def test_concat2():
     from sharpinference_b200.kernels import ops
     g = torch.Generator().manual_seed(2)
@@ -345,6 +366,21 @@ def test_greedy_generation_through_the_scheduler(folders, name):
         assert out == plain.generate_greedy(cfg, w, prompt, 12)
     m = eng.metrics()
     assert m["state_slots_free"] == 3 and all(g["held"] == 0 for g in m["cache_groups"].values())
+
+
+def test_command_line_generates_greedily(folders, capsys):
+    """``sharpi-cli`` on a Notedra folder: greedy tokens as JSON, with the per-layer trace switched on."""
+    import json
+
+    from sharpinference_b200 import cli
+    cfg, w = plain.load_folder(folders["R"])
+    prompt = traces.random_tokens(cfg["vocab"], 21, seed=9)
+    rc = cli.main(["-m", folders["R"], "--tokens", ",".join(map(str, prompt)), "-n", "6", "--temp", "0", "--dtype", "float32",
+                   "--repeat-penalty", "1.0", "--json", "--max-cache-tokens", "256", "--trace-layers"])
+    out = capsys.readouterr()
+    assert rc == 0
+    assert json.loads(out.out.strip().splitlines()[-1])["outputs"][0]["tokens"] == plain.generate_greedy(cfg, w, prompt, 6)
+    assert "layer 2" in out.err and "expert" in out.err
 
 
 def test_parts_are_registered_with_their_constants():
