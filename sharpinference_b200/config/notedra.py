@@ -11,7 +11,8 @@ A Notedra ``config.json`` describes the model layer by layer:
   same weights (null or absent: every layer runs once).
 
 No size stands in code; every layer may have sizes of its own.  An attention layer without ``mask`` sees every
-earlier position, one without ``rot`` is not rotated, and ``scale`` defaults to ``dim^(-1/2)``.
+earlier position, one without ``rot`` is not rotated, ``scale`` defaults to ``dim^(-1/2)``, ``kv_heads`` to
+``heads`` and ``vdim`` to ``dim``.
 """
 from __future__ import annotations
 
@@ -153,14 +154,15 @@ def _read_layer(entry, where: str, top: ConfigReader) -> Optional[NotedraLayer]:
         r.problem(f"key 'type': expected 'mlstm' or 'attention', found {kind!r}")
     elif kind is not None and mixer is not None:
         m = ConfigReader(mixer, f"{where}[mixer]")
-        heads, dim, vdim = m.int("heads"), m.int("dim"), m.int("vdim")
+        heads, dim = m.int("heads"), m.int("dim")
+        vdim = m.int("vdim", dim)
         fields = {}
         if kind == "mlstm":
             fields["gate_cap"] = m.float("gate_cap")
             if m.ok:
                 m.require(fields["gate_cap"] > 0, f"gate_cap must be positive, found {fields['gate_cap']}")
         else:
-            fields["kv_heads"] = m.int("kv_heads")
+            fields["kv_heads"] = m.int("kv_heads", heads)
             fields["scale"] = m.float("scale", None)
             rot, mask = m.object("rot", None), m.object("mask", None)
             if rot is not None:

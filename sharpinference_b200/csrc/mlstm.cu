@@ -85,9 +85,12 @@ __global__ void __launch_bounds__(32) mlstm_gates_kernel(MlstmArgs a) {
             zf = a.proj[(size_t)(t0 + 32 + lane) * a.ld + a.col_f + h];
         }
         float m_before = 0.0f, m_after = 0.0f;
-        for (int j = 0; j < n; ++j) {
+        // unrolled, so that the shuffles of all 32 rows are under way before the serial chain of additions and
+        // maxima needs them; rows beyond the request's end leave m as it is
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
             const float fj = __shfl_sync(0xffffffffu, fg, j), ij = __shfl_sync(0xffffffffu, ig, j);
-            const float m_new = fmaxf(fj + m, ij);
+            const float m_new = j < n ? fmaxf(fj + m, ij) : m;
             if (lane == j) { m_before = m; m_after = m_new; }
             m = m_new;
         }
@@ -116,37 +119,43 @@ __device__ __forceinline__ void copy_async_f32(float* dst_shared, const float* s
 __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-template <int RT>
-__global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a) {
+// CPT: value columns a thread holds (4, or 2 when the launch would otherwise leave SMs without a CTA: a CTA then
+// covers 16 columns and there are twice as many).  The state's layout does not depend on it.
+template <int RT, int CPT>
+__global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a, int col_blocks) {
     constexpr int DP = RT * 16;                         // padded key size
+    constexpr int CW = 8 * CPT;                         // value columns of a CTA
     constexpr int CHUNK = RT >= 16 ? MLSTM_CHUNK / 2 : MLSTM_CHUNK;      // rows staged at a time (48 KB of shared memory)
     constexpr int PER_THREAD = (CHUNK * DP) / SCAN_THREADS;              // staged k (and q) floats per thread
-    constexpr int V_PER_THREAD = (CHUNK * 32) / SCAN_THREADS;
+    constexpr int V_PER_THREAD = (CHUNK * CW + SCAN_THREADS - 1) / SCAN_THREADS;
     // two stages: while one chunk of rows is walked, the next one's keys, queries, values and coefficients arrive
     __shared__ __align__(16) float k_s[2][CHUNK * DP];
     __shared__ __align__(16) float q_s[2][CHUNK * DP];
-    __shared__ __align__(16) float v_s[2][CHUNK * 32];
+    __shared__ __align__(16) float v_s[2][CHUNK * CW];
     __shared__ float c_s[2][CHUNK * 2];                 // log a, log b
-    __shared__ __align__(16) float p_s[CHUNK * 16 * 32];      // [row][4 w + g][column]
-    const int b = blockIdx.x, h = blockIdx.y, slice = blockIdx.z;
+    __shared__ __align__(16) float p_s[CHUNK * 16 * CW];      // [row][4 w + g][column]
+    const int b = blockIdx.x, h = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int wg = warp * 4 + (lane >> 3), c4 = (lane & 7) * 4;
+    const int wg = warp * 4 + (lane >> 3), c4 = (lane & 7) * CPT;
     const int r0 = a.row_offsets[b], r1 = a.row_offsets[b + 1];
     if (r1 <= r0) return;
     const int d = a.d, dv = a.dv;
-    const bool norm_slice = slice == a.slices;          // the slice that carries n in its first column
+    const bool norm_slice = (int)blockIdx.z == col_blocks;      // the CTA that carries n in its first column
+    const int col0 = blockIdx.z * CW;                   // first value column of this CTA
     float* head = a.state + (size_t)a.state_slots[b] * a.state_stride + (size_t)h * a.head_stride;
-    float* st = head + (size_t)slice * d * 32;          // value slices: [d][32]; the normaliser: [d]
+    float* n_state = head + (size_t)a.slices * d * 32;
+    // value column x of the head lies in slice x / 32 of the state: [slices][d][32]
+    auto state_at = [&](int row, int x) -> float* { return head + ((size_t)(x >> 5) * d + row) * 32 + (x & 31); };
     const int row0 = wg * RT;
-    float S[RT][4];
+    float S[RT][CPT];
 #pragma unroll
     for (int i = 0; i < RT; ++i) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < CPT; ++j) {
             S[i][j] = 0.0f;
             if (row0 + i < d) {
-                if (!norm_slice) S[i][j] = st[(size_t)(row0 + i) * 32 + c4 + j];
-                else if (c4 + j == 0) S[i][j] = st[row0 + i];
+                if (!norm_slice) { if (col0 + c4 + j < a.slices * 32) S[i][j] = *state_at(row0 + i, col0 + c4 + j); }
+                else if (c4 + j == 0) S[i][j] = n_state[row0 + i];
             }
         }
     }
@@ -162,13 +171,15 @@ __global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a) {
         }
 #pragma unroll
         for (int j = 0; j < V_PER_THREAD; ++j) {
-            const int i = tid + j * SCAN_THREADS, t = i >> 5, x = i & 31;
-            if (norm_slice) {
-                v_s[stage][i] = (t < nc && x == 0) ? 1.0f : 0.0f;
-            } else {
-                const bool ok = t < nc && slice * 32 + x < dv;
-                copy_async_f32(&v_s[stage][i], a.proj + (size_t)(c0 + (ok ? t : 0)) * a.ld + a.col_v + h * dv +
-                                                   (ok ? slice * 32 + x : 0), ok);
+            const int i = tid + j * SCAN_THREADS, t = i / CW, x = i - t * CW;
+            if (i < CHUNK * CW) {
+                if (norm_slice) {
+                    v_s[stage][i] = (t < nc && x == 0) ? 1.0f : 0.0f;
+                } else {
+                    const bool ok = t < nc && col0 + x < dv;
+                    copy_async_f32(&v_s[stage][i], a.proj + (size_t)(c0 + (ok ? t : 0)) * a.ld + a.col_v + h * dv +
+                                                       (ok ? col0 + x : 0), ok);
+                }
             }
         }
         if (tid < CHUNK * 2) {
@@ -186,43 +197,47 @@ __global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a) {
         if (c0 + CHUNK < r1) fetch(c0 + CHUNK, stage ^ 1);
         for (int t = 0; t < nc; ++t) {
             const float ca = expf(c_s[stage][t * 2]), cb = expf(c_s[stage][t * 2 + 1]);
-            const float4 v4 = *reinterpret_cast<const float4*>(&v_s[stage][t * 32 + c4]);
-            const float bv[4] = {cb * v4.x, cb * v4.y, cb * v4.z, cb * v4.w};
+            float bv[CPT];
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) bv[j] = cb * v_s[stage][t * CW + c4 + j];
             const float* kt = &k_s[stage][t * DP + row0];
             const float* qt = &q_s[stage][t * DP + row0];
-            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float part[CPT];
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) part[j] = 0.0f;
 #pragma unroll
             for (int i = 0; i < RT; ++i) {
                 const float kk = kt[i], qq = qt[i];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < CPT; ++j) {
                     S[i][j] = fmaf(ca, S[i][j], kk * bv[j]);
                     part[j] = fmaf(S[i][j], qq, part[j]);
                 }
             }
-            *reinterpret_cast<float4*>(p_s + (t * 16 + wg) * 32 + c4) = make_float4(part[0], part[1], part[2], part[3]);
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) p_s[(t * 16 + wg) * CW + c4 + j] = part[j];
         }
         __syncthreads();
-        for (int idx = tid; idx < nc * 32; idx += SCAN_THREADS) {
-            const int t = idx >> 5, x = idx & 31;
+        for (int idx = tid; idx < nc * CW; idx += SCAN_THREADS) {
+            const int t = idx / CW, x = idx - t * CW;
             float sum = 0.0f;
 #pragma unroll
-            for (int w = 0; w < 16; ++w) sum += p_s[(t * 16 + w) * 32 + x];
+            for (int w = 0; w < 16; ++w) sum += p_s[(t * 16 + w) * CW + x];
             sum *= a.q_scale;                            // the query's factor, applied to the finished sum
             if (norm_slice) {
                 if (x == 0) a.nq[(size_t)(c0 + t) * a.heads + h] = sum;
-            } else if (slice * 32 + x < dv) {
-                a.o_raw[(size_t)(c0 + t) * a.heads * dv + h * dv + slice * 32 + x] = sum;
+            } else if (col0 + x < dv) {
+                a.o_raw[(size_t)(c0 + t) * a.heads * dv + h * dv + col0 + x] = sum;
             }
         }
     }
 #pragma unroll
     for (int i = 0; i < RT; ++i) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < CPT; ++j) {
             if (row0 + i < d) {
-                if (!norm_slice) st[(size_t)(row0 + i) * 32 + c4 + j] = S[i][j];
-                else if (c4 + j == 0) st[row0 + i] = S[i][j];
+                if (!norm_slice) { if (col0 + c4 + j < a.slices * 32) *state_at(row0 + i, col0 + c4 + j) = S[i][j]; }
+                else if (c4 + j == 0) n_state[row0 + i] = S[i][j];
             }
         }
     }
@@ -230,7 +245,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a) {
 
 template <int RT>
 static int launch_scan(const MlstmArgs& a, int B, cudaStream_t stream) {
-    mlstm_scan_kernel<RT><<<dim3(B, a.heads, a.slices + 1), SCAN_THREADS, 0, stream>>>(a);
+    // CTAs of 32 columns unless they would be fewer than the SMs (a single prompt portion): then of 16
+    const long long wide = (long long)B * a.heads * (a.slices + 1);
+    if (wide >= 148) {
+        mlstm_scan_kernel<RT, 4><<<dim3(B, a.heads, a.slices + 1), SCAN_THREADS, 0, stream>>>(a, a.slices);
+    } else {
+        const int blocks = (a.dv + 15) / 16;
+        mlstm_scan_kernel<RT, 2><<<dim3(B, a.heads, blocks + 1), SCAN_THREADS, 0, stream>>>(a, blocks);
+    }
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
@@ -265,6 +287,8 @@ SHARPI_API int sharpi_mlstm_recurrence(const float* proj, int ld, int col_q, int
 // out[t, h, :] = o[t, h, :] * rsqrt(mean(o[t, h, :]^2) + eps) * w[h, :] * sigmoid(gate[t, h, :])
 // One warp per (row, head).
 // ---------------------------------------------------------------------------------------
+constexpr int OUT_REGS = 8;      // value sizes up to 32 * OUT_REGS are held in registers by the out kernel
+
 template <typename TO>
 __global__ void mlstm_out_kernel(const float* __restrict__ o_raw, const float* __restrict__ nq,
                                  const float* __restrict__ coef, const float* __restrict__ gate, int gate_ld,
@@ -278,6 +302,32 @@ __global__ void mlstm_out_kernel(const float* __restrict__ o_raw, const float* _
     const float* o = o_raw + (size_t)t * heads * dv + (size_t)h * dv;
     const float* g = gate + (size_t)t * gate_ld + (size_t)h * dv;
     const float den = fmaxf(fabsf(nq[item]), expf(-coef[item * 4 + 2])) + 1e-6f;
+    TO* dst = out + (size_t)t * heads * dv + (size_t)h * dv;
+    if (dv <= 32 * OUT_REGS) {
+        // the head's values and gates in registers: every load is under way before the first is used
+        float v[OUT_REGS], gg[OUT_REGS], ww[OUT_REGS];
+#pragma unroll
+        for (int r = 0; r < OUT_REGS; ++r) {
+            const int c = lane + 32 * r;
+            v[r] = c < dv ? o[c] : 0.0f;
+            gg[r] = c < dv ? g[c] : 0.0f;
+            ww[r] = c < dv ? w[h * dv + c] : 0.0f;
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int r = 0; r < OUT_REGS; ++r) {
+            v[r] = v[r] / den;
+            ss = fmaf(v[r], v[r], ss);
+        }
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)dv + eps);
+#pragma unroll
+        for (int r = 0; r < OUT_REGS; ++r) {
+            const int c = lane + 32 * r;
+            if (c < dv) dst[c] = from_float<TO>(v[r] * scale * ww[r] * (1.0f / (1.0f + expf(-gg[r]))));
+        }
+        return;
+    }
     float ss = 0.0f;
     for (int c = lane; c < dv; c += 32) {
         const float v = o[c] / den;
@@ -285,7 +335,6 @@ __global__ void mlstm_out_kernel(const float* __restrict__ o_raw, const float* _
     }
     ss = warp_sum(ss);
     const float scale = 1.0f / sqrtf(ss / (float)dv + eps);
-    TO* dst = out + (size_t)t * heads * dv + (size_t)h * dv;
     for (int c = lane; c < dv; c += 32) {
         const float s = 1.0f / (1.0f + expf(-g[c]));
         dst[c] = from_float<TO>(o[c] / den * scale * w[h * dv + c] * s);

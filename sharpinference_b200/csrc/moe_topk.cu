@@ -2,8 +2,8 @@
 //
 //   router_topk   z = h Wr^T (float32), s = sigmoid(z); the k experts with the largest s + correction (the lowest
 //                 index among equals) are chosen; each weight is scale * s (without the correction), divided by the
-//                 sum of the chosen s first when `renormalize`.  One CTA per row: a row's logits are one fixed
-//                 sequence of additions whatever else the step holds.
+//                 sum of the chosen s first when `renormalize`.  A row's logits are one fixed sequence of additions
+//                 whatever else the step holds.
 //   pair_tokens   after the (row, choice) pairs have been sorted by expert: the row each sorted pair belongs to.
 //   combine       out[t] = add[t] + sum over the row's k pairs of y[pair], in the order of the choices.
 //
@@ -12,39 +12,70 @@
 #include "common.cuh"
 
 constexpr int TOPK_WARPS = 8;
+constexpr int TOPK_ROWS = 4;          // rows a CTA serves: a router row is fetched once for all of them
 
-// One CTA per row: warp w forms the logits of experts w, w + 8, ... (a lane adds its elements of the row in
-// ascending order in four interleaved chains, the chains and then the lanes are added in a fixed order), then
-// warp 0 picks the k best.
+// One CTA per TOPK_ROWS rows: warp w forms the logits of experts w, w + 8, ... for each of the CTA's rows (a lane
+// adds its elements of a row in ascending order in four interleaved chains, the chains and then the lanes are added
+// in a fixed order: a row's logits do not depend on its neighbours), then warp r picks the k best of row r.
 __global__ void __launch_bounds__(TOPK_WARPS * 32)
 router_topk_kernel(const float* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ correction,
-                   int H, int E, int k, float scale, int renormalize, int* __restrict__ expert_id,
-                   float* __restrict__ weight, float* __restrict__ scores_out) {
-    extern __shared__ float smem[];                       // s [E], choice [E]
+                   int T, int H, int E, int k, float scale, int renormalize, int* __restrict__ expert_id,
+                   float* __restrict__ weight, float* __restrict__ scores_out, int stage_rows) {
+    extern __shared__ float smem[];                       // per row s [E], choice [E]; then the rows [ROWS][H] if they fit
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x;
-    float* s_s = smem;
-    float* c_s = s_s + E;
-    const float* row = h + (size_t)t * H;
+    const int t0 = blockIdx.x * TOPK_ROWS;
+    const int rows = min(TOPK_ROWS, T - t0);
+    const float* row[TOPK_ROWS];
+#pragma unroll
+    for (int r = 0; r < TOPK_ROWS; ++r) row[r] = h + (size_t)(t0 + min(r, rows - 1)) * H;
+    if (stage_rows) {                                     // the rows are read from memory once, by all warps together
+        float* rows_s = smem + (size_t)TOPK_ROWS * 2 * E;
+        for (int i = threadIdx.x; i < rows * H; i += TOPK_WARPS * 32) rows_s[i] = h[(size_t)t0 * H + i];
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < TOPK_ROWS; ++r) row[r] = rows_s + (size_t)min(r, rows - 1) * H;
+    }
     for (int e = warp; e < E; e += TOPK_WARPS) {
         const float* w = wr + (size_t)e * H;
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float acc[TOPK_ROWS][4];
+#pragma unroll
+        for (int r = 0; r < TOPK_ROWS; ++r)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[r][u] = 0.0f;
         int i = lane;
         for (; i + 96 < H; i += 128) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) acc[u] = fmaf(row[i + 32 * u], w[i + 32 * u], acc[u]);
+            for (int u = 0; u < 4; ++u) {
+                const float wv = w[i + 32 * u];
+#pragma unroll
+                for (int r = 0; r < TOPK_ROWS; ++r) acc[r][u] = fmaf(row[r][i + 32 * u], wv, acc[r][u]);
+            }
         }
-        for (int u = 0; i < H; i += 32, ++u) acc[u] = fmaf(row[i], w[i], acc[u]);
-        const float z = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-        if (lane == 0) {
-            const float s = 1.0f / (1.0f + expf(-z));
-            s_s[e] = s;
-            c_s[e] = correction ? s + correction[e] : s;
-            if (scores_out) scores_out[(size_t)t * E + e] = s;
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {                      // what is left: up to three more elements a lane
+            const int ii = i + 32 * u;
+            if (ii < H) {
+                const float wv = w[ii];
+#pragma unroll
+                for (int r = 0; r < TOPK_ROWS; ++r) acc[r][u] = fmaf(row[r][ii], wv, acc[r][u]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < TOPK_ROWS; ++r) {
+            const float z = warp_sum((acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]));
+            if (lane == 0 && r < rows) {
+                const float s = 1.0f / (1.0f + expf(-z));
+                smem[(size_t)r * 2 * E + e] = s;
+                smem[(size_t)r * 2 * E + E + e] = correction ? s + correction[e] : s;
+                if (scores_out) scores_out[(size_t)(t0 + r) * E + e] = s;
+            }
         }
     }
     __syncthreads();
-    if (warp != 0) return;
+    if (warp >= rows) return;
+    const int t = t0 + warp;
+    float* s_s = smem + (size_t)warp * 2 * E;
+    float* c_s = s_s + E;
     float total = 0.0f;
     int mine = 0;                                          // lane j keeps the j-th choice
     for (int j = 0; j < k; ++j) {
@@ -78,10 +109,12 @@ SHARPI_API int sharpi_router_topk(const float* h, const float* wr, const float* 
                                   cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (H <= 0 || E <= 0 || k <= 0 || k > E || k > 32) return SHARPI_BAD_ARGUMENT;
-    const size_t smem = (size_t)2 * E * sizeof(float);
+    size_t smem = (size_t)TOPK_ROWS * 2 * E * sizeof(float);
     if (smem > 48 * 1024) return SHARPI_BAD_ARGUMENT;
-    router_topk_kernel<<<T, TOPK_WARPS * 32, smem, stream>>>(h, wr, correction, H, E, k, scale, renormalize, expert_id,
-                                                              weight, scores_out);
+    const int stage_rows = smem + (size_t)TOPK_ROWS * H * sizeof(float) <= 48 * 1024;
+    if (stage_rows) smem += (size_t)TOPK_ROWS * H * sizeof(float);
+    router_topk_kernel<<<(T + TOPK_ROWS - 1) / TOPK_ROWS, TOPK_WARPS * 32, smem, stream>>>(
+        h, wr, correction, T, H, E, k, scale, renormalize, expert_id, weight, scores_out, stage_rows);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
@@ -109,10 +142,30 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* add
     }
 }
 
+__global__ void moe_combine_vec4_kernel(const float4* __restrict__ y, const float4* add, float4* out, int k, int H4) {
+    const int t = blockIdx.x;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H4; i += gridDim.y * blockDim.x) {
+        float4 acc = add ? add[(size_t)t * H4 + i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int j = 0; j < k; ++j) {
+            const float4 v = y[((size_t)t * k + j) * H4 + i];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        out[(size_t)t * H4 + i] = acc;
+    }
+}
+
 SHARPI_API int sharpi_moe_combine(const float* y, const float* add, float* out, int T, int k, int H,
                                   cudaStream_t stream) {
     if (T <= 0 || H <= 0) return SHARPI_OK;
     if (k <= 0) return SHARPI_BAD_ARGUMENT;
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(add) | reinterpret_cast<uintptr_t>(out);
+    if (H % 4 == 0 && (ptrs & 15) == 0) {               // same additions in the same order, four columns a thread
+        int by4 = (H / 4 + 255) / 256;
+        if (by4 > 64) by4 = 64;
+        moe_combine_vec4_kernel<<<dim3(T, by4), 256, 0, stream>>>((const float4*)y, (const float4*)add, (float4*)out, k, H / 4);
+        SHARPI_CHECK_LAUNCH();
+        return SHARPI_OK;
+    }
     int by = (H + 255) / 256;
     if (by > 64) by = 64;
     moe_combine_kernel<<<dim3(T, by), 256, 0, stream>>>(y, add, out, k, H);

@@ -52,8 +52,11 @@ def test_defaults_of_absent_keys():
     assert free.window == 0 and free.rot_dims == 0
     case = copy.deepcopy(CASE_Q)
     del case["layers"][2]["mixer"]["scale"]
+    del case["layers"][2]["mixer"]["kv_heads"]
+    del case["layers"][2]["mixer"]["vdim"]
     _, cfg = resolve(case, "test")
     assert cfg.layers[2].scale == pytest.approx(32 ** -0.5)
+    assert cfg.layers[2].kv_heads == 4 and cfg.layers[2].vdim == 32
 
 
 def test_config_problems_are_listed_together():
