@@ -12,11 +12,13 @@
 #include "common.cuh"
 
 constexpr int TOPK_WARPS = 8;
-constexpr int TOPK_ROWS = 4;          // rows a CTA serves: a router row is fetched once for all of them
+constexpr int TOPK_MANY_ROWS = 512;   // steps of more rows than this put four rows in a CTA (a router row is fetched
+                                      // once for all of them); smaller steps one, for more CTAs
 
-// One CTA per TOPK_ROWS rows: warp w forms the logits of experts w, w + 8, ... for each of the CTA's rows (a lane
+// One CTA per TOPK_ROWS rows (1 or 4): warp w forms the logits of experts w, w + 8, ... for each of the CTA's rows (a lane
 // adds its elements of a row in ascending order in four interleaved chains, the chains and then the lanes are added
 // in a fixed order: a row's logits do not depend on its neighbours), then warp r picks the k best of row r.
+template <int TOPK_ROWS>
 __global__ void __launch_bounds__(TOPK_WARPS * 32)
 router_topk_kernel(const float* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ correction,
                    int T, int H, int E, int k, float scale, int renormalize, int* __restrict__ expert_id,
@@ -109,12 +111,17 @@ SHARPI_API int sharpi_router_topk(const float* h, const float* wr, const float* 
                                   cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (H <= 0 || E <= 0 || k <= 0 || k > E || k > 32) return SHARPI_BAD_ARGUMENT;
-    size_t smem = (size_t)TOPK_ROWS * 2 * E * sizeof(float);
+    const int per_cta = T > TOPK_MANY_ROWS ? 4 : 1;
+    size_t smem = (size_t)per_cta * 2 * E * sizeof(float);
     if (smem > 48 * 1024) return SHARPI_BAD_ARGUMENT;
-    const int stage_rows = smem + (size_t)TOPK_ROWS * H * sizeof(float) <= 48 * 1024;
-    if (stage_rows) smem += (size_t)TOPK_ROWS * H * sizeof(float);
-    router_topk_kernel<<<(T + TOPK_ROWS - 1) / TOPK_ROWS, TOPK_WARPS * 32, smem, stream>>>(
-        h, wr, correction, T, H, E, k, scale, renormalize, expert_id, weight, scores_out, stage_rows);
+    const int stage_rows = smem + (size_t)per_cta * H * sizeof(float) <= 48 * 1024;
+    if (stage_rows) smem += (size_t)per_cta * H * sizeof(float);
+    if (per_cta == 4)
+        router_topk_kernel<4><<<(T + 3) / 4, TOPK_WARPS * 32, smem, stream>>>(
+            h, wr, correction, T, H, E, k, scale, renormalize, expert_id, weight, scores_out, stage_rows);
+    else
+        router_topk_kernel<1><<<T, TOPK_WARPS * 32, smem, stream>>>(
+            h, wr, correction, T, H, E, k, scale, renormalize, expert_id, weight, scores_out, stage_rows);
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
