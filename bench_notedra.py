@@ -2,10 +2,10 @@
 resemble a real model's, beside Llama 4 (the framework's other architecture) at equal width, depth and head sizes,
 both with random bfloat16 weights on one B200.
 
-Per width W: Notedra has six layers (mlstm, attention, mlstm, mlstm, attention, mlstm) of which the middle four run
-twice (ten layer runs); matrix-memory heads of key size 128 and value size 256 (W / 256 of them), attention heads of
-size 128 (W / 128, a quarter as many key/value heads) under a window of 1024 positions, a dense feed-forward of 4 W
-on the first layer and 16 experts of W / 2 with two a row on the others.  Llama 4 has ten layers of the same
+Per width W: Notedra has five layers (attention, mlstm, mlstm, attention, mlstm) that all run twice (ten layer
+runs); matrix-memory heads of key size 128 and value size 256 (W / 256 of them), attention heads of size 128 (W /
+128, a quarter as many key/value heads) under a window of 1024 positions, a dense feed-forward of 4 W on the
+second layer and 16 experts of W / 2 with two a row on the others.  Llama 4 has ten layers of the same
 attention sizes under a chunk of 1024 positions, 16 experts of W / 2 with one a row plus the shared expert.
 
 Timed with CUDA events after warm-up; every step's weights, state and cache exceed the L2 cache.  Prefill: one
@@ -22,13 +22,13 @@ def notedra_config(W: int, vocab: int = 32768) -> dict:
     mh, ah = max(1, W // 256), max(1, W // 128)
     mlstm = {"heads": mh, "dim": 128, "vdim": 256, "gate_cap": 15.0}
     attn = {"heads": ah, "kv_heads": max(1, ah // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-            "rot": {"dims": 64, "base": 10000.0}, "mask": {"size": 1024}}
-    moe = {"kind": "moe", "expert": {"ff": W // 2}, "router": {"experts": 16, "top": 2, "scale": 2.5}}
-    kinds = ["mlstm", "attention", "mlstm", "mlstm", "attention", "mlstm"]
+            "rot": {"dims": 64, "base": 500000.0}, "mask": {"size": 1024}}
+    moe = {"kind": "moe", "expert": {"ff": W // 2}, "router": {"experts": 16, "top": 2, "scale": 2.0}}
+    kinds = ["attention", "mlstm", "mlstm", "attention", "mlstm"]
     layers = [{"type": k, "mixer": dict(mlstm if k == "mlstm" else attn),
-               "mlp": {"kind": "dense", "ff": 4 * W} if i == 0 else dict(moe)} for i, k in enumerate(kinds)]
-    return {"architecture": "Notedra", "vocab": vocab, "width": W, "norm": {"eps": 1e-5}, "layers": layers,
-            "loop": {"start": 1, "stop": 5, "times": 2}}
+               "mlp": {"kind": "dense", "ff": 4 * W} if i == 1 else dict(moe)} for i, k in enumerate(kinds)]
+    return {"architecture": "Notedra", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "layers": layers,
+            "loop": {"start": 0, "stop": 5, "times": 2}}
 
 
 def llama4_config(W: int, vocab: int = 32768) -> dict:

@@ -17,7 +17,7 @@
 // Three kernels, all reading the step through device arrays only (row_offsets, state_slots):
 //   gates   one warp per (request, head) walks the request's rows in order, 32 at a time: lane j forms the capped
 //           gates of row j (tanh, logsigmoid), then every lane runs the same 32 steps of m_t = max(f_t + m_{t-1}, i_t)
-//           on values handed round by shuffles (one addition and one maximum a row on the serial path), and lane j
+//           on values passed along by shuffles (one addition and one maximum a row on the serial path), and lane j
 //           leaves log a_t, log b_t and m_t of its row.  It owns m of the state.
 //   scan    one CTA of 128 threads per (request, head, slice of 32 value columns) walks the rows in order with its
 //           [d, 32] slice of S in registers: a thread holds d / 16 rows of four neighbouring columns, so that every
