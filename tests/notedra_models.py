@@ -67,7 +67,36 @@ CASE_R = {
     "loop": {"start": 1, "stop": 3, "times": 1},
 }
 
-CASES = {"P": (CASE_P, 0.12, 11), "Q": (CASE_Q, 0.1, 12), "R": (CASE_R, 0.15, 13)}      # config, std of the weights, seed
+# S: ones and twos wherever a size can be one or two: one head, one key/value head, a head of two elements, a window
+# of one position (a token sees itself only) and of two, one expert, a loop of one layer run four times, a dense
+# network one wide.
+CASE_S = {
+    "architecture": "Notedra", "vocab": 23, "width": 16, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "attention", "mixer": _attn(1, 1, 2, 6, 1.5, window=1, rot=(2, 10.0)), "mlp": _moe(1, 1, 8, 1.0)},
+        {"type": "mlstm", "mixer": {"heads": 1, "dim": 2, "vdim": 1, "gate_cap": 5.0}, "mlp": {"kind": "dense", "ff": 1}},
+        {"type": "attention", "mixer": _attn(2, 1, 4, 2, 0.9, window=2, rot=(2, 7.0)), "mlp": _moe(2, 2, 3, 0.5)},
+    ],
+    "loop": {"start": 1, "stop": 2, "times": 4},
+}
+
+# T: the largest heads: a matrix memory with keys of 256 and of 136 elements, attention heads of 128 (the tcgen05
+# prompt kernel) under a window of exactly one page and of 256 (no tensor-core attention kernel takes them), rotated
+# in part.
+CASE_T = {
+    "architecture": "Notedra", "vocab": 50, "width": 128, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "mlstm", "mixer": {"heads": 1, "dim": 256, "vdim": 24, "gate_cap": 20.0}, "mlp": None},
+        {"type": "attention", "mixer": _attn(2, 1, 128, 128, 0.05, window=64, rot=(96, 10000.0)), "mlp": _moe(3, 2, 64, 1.0)},
+        {"type": "mlstm", "mixer": {"heads": 2, "dim": 136, "vdim": 72, "gate_cap": 12.0}, "mlp": {"kind": "dense", "ff": 48}},
+        {"type": "attention", "mixer": _attn(1, 1, 256, 32, 0.03, window=100, rot=(256, 1000.0)), "mlp": None},
+    ],
+    "loop": {"start": 0, "stop": 4, "times": 2},
+}
+
+# config, std of the weights, seed
+CASES = {"P": (CASE_P, 0.12, 11), "Q": (CASE_Q, 0.1, 12), "R": (CASE_R, 0.15, 13), "S": (CASE_S, 0.4, 14),
+         "T": (CASE_T, 0.08, 15)}
 
 
 def write(name: str, out_dir: str) -> str:

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_notedra as plain
-from notedra_models import CASE_P, CASE_Q, CASE_R, CASES, write
+from notedra_models import CASE_P, CASE_Q, CASE_R, CASE_S, CASE_T, CASES, write
 
 from sharpinference_b200.config import ConfigError, NotedraConfig
 from sharpinference_b200.registry import get_architecture, resolve
@@ -17,7 +17,7 @@ from sharpinference_b200.weights.loading import declared_tensors
 
 
 # -- configuration -------------------------------------------------------------------------
-@pytest.mark.parametrize("case", [CASE_P, CASE_Q, CASE_R])
+@pytest.mark.parametrize("case", [CASE_P, CASE_Q, CASE_R, CASE_S, CASE_T])
 def test_config_round_trip(case):
     arch, cfg = resolve(copy.deepcopy(case), "test")
     assert arch.name == "Notedra" and isinstance(cfg, NotedraConfig)

@@ -16,7 +16,8 @@ DEV = "cuda:0"
 TOL = {"float32": 5e-5, "bfloat16": 3e-2}
 # An expert choice that differs from the plain implementation's must be a near-tie of the choice scores.
 MARGIN = 2e-2
-LENGTHS = {"P": [1, 9, 40, 83, 150, 2], "Q": [150, 5, 67, 200, 31], "R": [3, 70, 12, 45, 100, 64, 65]}
+LENGTHS = {"P": [1, 9, 40, 83, 150, 2], "Q": [150, 5, 67, 200, 31], "R": [3, 70, 12, 45, 100, 64, 65],
+           "S": [1, 2, 30, 5], "T": [140, 66, 3, 129]}
 
 
 def requests_for(name):
@@ -64,6 +65,42 @@ def reference_for(folder, reqs, routing, fallback, dtype):
     return ref
 
 
+# Case T has a position at which rounding alone is amplified beyond TOL (the matrix memory divides by a normaliser
+# that passes close to its floor there): in bfloat16 a position's limit is the larger of TOL and three times the
+# error that rounding the normed activations to bfloat16 causes in the plain model at that position.
+_noise = {}
+
+
+def rounding_noise(folder, name):
+    if name not in _noise:
+        cfg, w = plain.load_folder(folder)
+        plain_norm = plain.offset_norm
+        out = {}
+        try:
+            for rid, toks in requests_for(name).items():
+                exact = plain.forward(cfg, w, toks)
+                plain.offset_norm = lambda x, ww, eps: plain_norm(x, ww, eps).to(torch.bfloat16).to(plain.DT)
+                rounded = plain.forward(cfg, w, toks)
+                plain.offset_norm = plain_norm
+                out[rid] = (rounded - exact).abs().max(dim=1).values / exact.abs().max()
+        finally:
+            plain.offset_norm = plain_norm
+        _noise[name] = out
+    return _noise[name]
+
+
+def within_limits(got, ref, dtype, noise=None):
+    """Every wanted row against the reference, relative to the largest |logit| of its request."""
+    worst, where = 0.0, None
+    for (rid, pos), row in got.items():
+        scale = float(ref[rid].abs().max())
+        err = float((row.double() - ref[rid][pos].double()).abs().max()) / scale
+        limit = TOL[dtype] if noise is None else max(TOL[dtype], 3.0 * float(noise[rid][pos]))
+        if not err / limit <= worst:
+            worst, where = err / limit, (rid, pos, err)
+    return worst, where
+
+
 def run_and_compare(folder, name, dtype, steps, expected, page_size=None, max_batch=4):
     reqs = requests_for(name)
     eng = engine_for(folder, dtype, traces.max_tokens(steps, page_size or 64), max_batch=max_batch, page_size=page_size)
@@ -75,8 +112,9 @@ def run_and_compare(folder, name, dtype, steps, expected, page_size=None, max_ba
     wanted = sum(len(e["want"]) for st in steps for e in st["entries"])
     assert len({rid for rid, _ in got}) == len(reqs) and len(got) == wanted
     ref = reference_for(folder, reqs, routing, expected[name], dtype)
-    err, where = traces.worst_error(got, ref)
-    assert err < TOL[dtype], f"{name} {dtype}: worst relative error {err:.3e} at {where}"
+    noise = rounding_noise(folder, name) if (dtype == "bfloat16" and name == "T") else None
+    ratio, where = within_limits(got, ref, dtype, noise)
+    assert ratio < 1.0, f"{name} {dtype}: error over its limit ({ratio:.2f} of it) at {where}"
     return eng
 
 
@@ -303,7 +341,7 @@ def test_one_slot_used_again_starts_from_zero(folders, expected, name):
         assert err < TOL["float32"], (rid, err, where)
 
 
-@pytest.mark.parametrize("name", ["P", "R"])
+@pytest.mark.parametrize("name", ["P", "R", "T"])
 def test_a_window_one_position_off_would_show(folders, expected, name):
     """The comparison is sharp enough: the plain model with every window one position longer or shorter differs
     from the engine by far more than the tolerance once a sequence is longer than the window, in prompts and in
@@ -320,8 +358,9 @@ def test_a_window_one_position_off_would_show(folders, expected, name):
         scale = float(right["r"].abs().max())
         early = min(windows) - 1
         assert float((wrong[:early] - right["r"][:early]).abs().max()) / scale < 1e-9
-        late_prompt = float((wrong[early + 2:60] - right["r"][early + 2:60]).abs().max()) / scale
-        late_decode = float((wrong[60:] - right["r"][60:]).abs().max()) / scale
+        cut = max(60, early + 10)                         # the last 60 tokens are decoded one by one
+        late_prompt = float((wrong[early + 2:cut] - right["r"][early + 2:cut]).abs().max()) / scale
+        late_decode = float((wrong[cut:] - right["r"][cut:]).abs().max()) / scale
         assert late_prompt > 100 * TOL["float32"] and late_decode > 100 * TOL["float32"], (shift, late_prompt, late_decode)
 
 
