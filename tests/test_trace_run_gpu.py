@@ -107,6 +107,22 @@ def test_whole_equals_decoded_tail_in_the_program(model_dirs, tmp_path):
         assert torch.allclose(got_whole[key], got_tail[key], rtol=0, atol=1e-6 * float(got_whole[key].abs().max()))
 
 
+def test_notedra_mixed_trace_through_the_program(tmp_path):
+    """The second architecture through the same program: six requests, at most four live at a time for the
+    program's four state slots, portions beside single tokens, a pool sized for the schedule's peak."""
+    import notedra_models
+    import plain_notedra
+    folder = notedra_models.write("P", str(tmp_path / "model"))
+    cfg, w = plain_notedra.load_folder(folder)
+    reqs = {f"n{i}": traces.random_tokens(cfg["vocab"], n, seed=17 * i + n) for i, n in enumerate([80, 3, 150, 41, 66, 9])}
+    steps = traces.mixed(reqs, max_live=4)
+    got, vocab = run_trace(folder, "float32", steps, tmp_path / "out")
+    assert vocab == cfg["vocab"]
+    ref = {rid: plain_notedra.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    err, where = traces.worst_error(got, ref)
+    assert err < 5e-5, (err, where)
+
+
 def test_bad_input_fails_loudly(model_dirs, tmp_path):
     cmd = [os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["A"], "--dtype", "float32", "--out",
            str(tmp_path), "--max-tokens", "64"]
