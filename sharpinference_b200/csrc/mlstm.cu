@@ -35,7 +35,7 @@
 #include "common.cuh"
 
 constexpr int MLSTM_CHUNK = 8;       // rows staged in shared memory at a time (half as many at the largest key size)
-constexpr int MLSTM_MAX_D = 256;     // key/query size the kernels take
+constexpr int MLSTM_MAX_D = 512;     // key/query size the kernels take
 
 struct MlstmArgs {
     const float* proj;       // [T, ld] fused projections of the step's rows
@@ -279,7 +279,8 @@ SHARPI_API int sharpi_mlstm_recurrence(const float* proj, int ld, int col_q, int
     if (d <= 32) return launch_scan<2>(a, B, stream);
     if (d <= 64) return launch_scan<4>(a, B, stream);
     if (d <= 128) return launch_scan<8>(a, B, stream);
-    return launch_scan<16>(a, B, stream);
+    if (d <= 256) return launch_scan<16>(a, B, stream);
+    return launch_scan<32>(a, B, stream);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -725,7 +725,7 @@ def moe_combine(y_pairs: torch.Tensor, k: int, *, add: Optional[torch.Tensor] = 
     return out
 
 
-MLSTM_MAX_KEY_SIZE = 256
+MLSTM_MAX_KEY_SIZE = 512
 
 
 def mlstm_state_floats(heads: int, d: int, dv: int):

@@ -215,7 +215,8 @@ def test_pair_tokens_and_combine():
     assert out.data_ptr() == add.data_ptr() and torch.allclose(add.double().cpu(), want, atol=1e-5)
 
 
-@pytest.mark.parametrize("heads,d,dv", [(3, 24, 40), (1, 8, 8), (2, 64, 100), (2, 200, 33), (2, 16, 32)])
+@pytest.mark.parametrize("heads,d,dv", [(3, 24, 40), (1, 8, 8), (2, 64, 100), (2, 200, 33), (2, 16, 32), (1, 512, 40),
+                                        (2, 2, 1)])
 def test_mlstm_recurrence_kernel(heads, d, dv):
     """Three requests of unequal length in one step, then a second step that goes on from the state (one of the
     requests sits it out, one brings a single row), against the plain recurrence; gates over their whole range."""
