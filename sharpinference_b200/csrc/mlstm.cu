@@ -15,9 +15,10 @@
 // by a weight and by sigmoid of an output gate.
 //
 // Three kernels, all reading the step through device arrays only (row_offsets, state_slots):
-//   gates   one warp per (request, head) walks the request's rows in order, 32 at a time: lane j forms the capped
-//           gates of row j (tanh, logsigmoid), then every lane runs the same 32 steps of m_t = max(f_t + m_{t-1}, i_t)
-//           on values passed along by shuffles (one addition and one maximum a row on the serial path), and lane j
+//   gates   one warp per (request, head) walks the request's rows in order, 32 at a time: lane j holds the capped
+//           gates of row j (tanh, logsigmoid; formed here, or for steps of many rows by a kernel over all rows at
+//           once ahead of the walk), then every lane runs the same 32 steps of m_t = max(f_t + m_{t-1}, i_t) on
+//           values passed along by shuffles (one addition and one maximum a row on the serial path), and lane j
 //           leaves log a_t, log b_t and m_t of its row.  It owns m of the state.
 //   scan    one CTA of 128 threads per (request, head, slice of 32 value columns) walks the rows in order with its
 //           [d, 32] slice of S in registers: a thread holds d / 16 rows of four neighbouring columns, so that every
@@ -61,8 +62,28 @@ __device__ __forceinline__ float log_sigmoid(float x) {
 }
 
 // ---------------------------------------------------------------------------------------
-// gates: grid (B, heads), one warp
+// gates: grid (B, heads), one warp.  PRE: the capped gates of every row were formed by gate_values_kernel (all rows
+// in parallel) and lie in coef[.., 0] and coef[.., 1]; otherwise the warp forms them itself (steps of few rows: one
+// launch fewer).  The arithmetic is the same either way.
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void capped_gates(float zi, float zf, float bi, float bf, float cap, float& ig, float& fg) {
+    ig = cap * tanhf((zi + bi) / cap);
+    fg = log_sigmoid(cap * tanhf((zf + bf) / cap));
+}
+
+__global__ void gate_values_kernel(MlstmArgs a, long long items) {
+    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= items) return;
+    const long long t = item / a.heads;
+    const int h = (int)(item - t * a.heads);
+    float ig, fg;
+    capped_gates(a.proj[(size_t)t * a.ld + a.col_i + h], a.proj[(size_t)t * a.ld + a.col_f + h], a.bias_i[h], a.bias_f[h],
+                 a.cap, ig, fg);
+    a.coef[item * 4] = ig;
+    a.coef[item * 4 + 1] = fg;
+}
+
+template <bool PRE>
 __global__ void __launch_bounds__(32) mlstm_gates_kernel(MlstmArgs a) {
     const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
     const int r0 = a.row_offsets[b], r1 = a.row_offsets[b + 1];
@@ -71,19 +92,27 @@ __global__ void __launch_bounds__(32) mlstm_gates_kernel(MlstmArgs a) {
                      (size_t)a.slices * a.d * 32 + a.d;
     float m = *m_state;
     const float bi = a.bias_i[h], bf = a.bias_f[h];
-    float zi = 0.0f, zf = 0.0f;
-    if (r0 + lane < r1) {
-        zi = a.proj[(size_t)(r0 + lane) * a.ld + a.col_i + h];
-        zf = a.proj[(size_t)(r0 + lane) * a.ld + a.col_f + h];
-    }
+    // x, y: the raw gate projections of this lane's row, or (PRE) its finished gates
+    auto fetch = [&](int r, float& x, float& y) {
+        x = 0.0f;
+        y = 0.0f;
+        if (r < r1) {
+            if (PRE) {
+                x = a.coef[((size_t)r * a.heads + h) * 4];
+                y = a.coef[((size_t)r * a.heads + h) * 4 + 1];
+            } else {
+                x = a.proj[(size_t)r * a.ld + a.col_i + h];
+                y = a.proj[(size_t)r * a.ld + a.col_f + h];
+            }
+        }
+    };
+    float x, y;
+    fetch(r0 + lane, x, y);
     for (int t0 = r0; t0 < r1; t0 += 32) {
         const int n = min(32, r1 - t0);
-        const float ig = a.cap * tanhf((zi + bi) / a.cap);
-        const float fg = log_sigmoid(a.cap * tanhf((zf + bf) / a.cap));
-        if (t0 + 32 + lane < r1) {                       // the next 32 rows' raw gates, while these are walked
-            zi = a.proj[(size_t)(t0 + 32 + lane) * a.ld + a.col_i + h];
-            zf = a.proj[(size_t)(t0 + 32 + lane) * a.ld + a.col_f + h];
-        }
+        float ig = x, fg = y;
+        if (!PRE) capped_gates(x, y, bi, bf, a.cap, ig, fg);
+        fetch(t0 + 32 + lane, x, y);                     // the next 32 rows, while these are walked
         float m_before = 0.0f, m_after = 0.0f;
         // unrolled, so that the shuffles of all 32 rows are under way before the serial chain of additions and
         // maxima needs them; rows beyond the request's end leave m as it is
@@ -195,8 +224,16 @@ __global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a, i
         copy_async_wait_all();
         __syncthreads();              // this chunk has arrived; the other stage and the partial sums have been read
         if (c0 + CHUNK < r1) fetch(c0 + CHUNK, stage ^ 1);
-        for (int t = 0; t < nc; ++t) {
-            const float ca = expf(c_s[stage][t * 2]), cb = expf(c_s[stage][t * 2 + 1]);
+        float ea[CHUNK], eb[CHUNK];                      // a_t and b_t of the chunk, ahead of the serial walk
+#pragma unroll
+        for (int t = 0; t < CHUNK; ++t) {
+            ea[t] = expf(c_s[stage][t * 2]);
+            eb[t] = expf(c_s[stage][t * 2 + 1]);
+        }
+#pragma unroll
+        for (int t = 0; t < CHUNK; ++t) {
+            if (t >= nc) break;
+            const float ca = ea[t], cb = eb[t];
             float bv[CPT];
 #pragma unroll
             for (int j = 0; j < CPT; ++j) bv[j] = cb * v_s[stage][t * CW + c4 + j];
@@ -245,9 +282,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a, i
 
 template <int RT>
 static int launch_scan(const MlstmArgs& a, int B, cudaStream_t stream) {
-    // CTAs of 32 columns unless they would be fewer than the SMs (a single prompt portion): then of 16
-    const long long wide = (long long)B * a.heads * (a.slices + 1);
-    if (wide >= 148) {
+    // CTAs of 32 columns unless they would be fewer than the SMs (a single prompt portion): then of 16.  (CTAs of 8
+    // columns, twice as many again, measured slower: 488 against 390 us for one portion of 2048 rows, 8 heads.)
+    if ((long long)B * a.heads * (a.slices + 1) >= 148) {
         mlstm_scan_kernel<RT, 4><<<dim3(B, a.heads, a.slices + 1), SCAN_THREADS, 0, stream>>>(a, a.slices);
     } else {
         const int blocks = (a.dv + 15) / 16;
@@ -273,7 +310,14 @@ SHARPI_API int sharpi_mlstm_recurrence(const float* proj, int ld, int col_q, int
     a.state = state; a.state_stride = state_stride; a.head_stride = head_stride; a.heads = heads; a.d = d; a.dv = dv;
     a.slices = (dv + 31) / 32; a.cap = cap; a.q_scale = q_scale; a.coef = coef; a.o_raw = o_raw; a.nq = nq;
     if ((long long)head_stride < (long long)a.slices * d * 32 + d + 1) return SHARPI_BAD_ARGUMENT;
-    mlstm_gates_kernel<<<dim3(B, heads), 32, 0, stream>>>(a);
+    if (T > 256) {                   // many rows: the gates' tanh and logsigmoid for all rows at once, ahead of the walk
+        const long long items = (long long)T * heads;
+        gate_values_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(a, items);
+        SHARPI_CHECK_LAUNCH();
+        mlstm_gates_kernel<true><<<dim3(B, heads), 32, 0, stream>>>(a);
+    } else {
+        mlstm_gates_kernel<false><<<dim3(B, heads), 32, 0, stream>>>(a);
+    }
     SHARPI_CHECK_LAUNCH();
     if (d <= 16) return launch_scan<1>(a, B, stream);
     if (d <= 32) return launch_scan<2>(a, B, stream);
