@@ -177,15 +177,30 @@ __global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a, i
     auto state_at = [&](int row, int x) -> float* { return head + ((size_t)(x >> 5) * d + row) * 32 + (x & 31); };
     const int row0 = wg * RT;
     float S[RT][CPT];
+    // a thread's CPT columns are neighbours inside one slice: one 16-byte (CPT = 4) or 8-byte (CPT = 2) access a row
+    // when the state's strides keep that alignment (key sizes that are multiples of four: the common case)
+    const bool wide = CPT > 1 && !norm_slice && col0 + c4 + CPT <= a.slices * 32 &&
+                      (reinterpret_cast<uintptr_t>(state_at(0, col0 + c4)) & (CPT * 4 - 1)) == 0;
 #pragma unroll
     for (int i = 0; i < RT; ++i) {
 #pragma unroll
-        for (int j = 0; j < CPT; ++j) {
-            S[i][j] = 0.0f;
-            if (row0 + i < d) {
-                if (!norm_slice) { if (col0 + c4 + j < a.slices * 32) S[i][j] = *state_at(row0 + i, col0 + c4 + j); }
-                else if (c4 + j == 0) S[i][j] = n_state[row0 + i];
+        for (int j = 0; j < CPT; ++j) S[i][j] = 0.0f;
+        if (row0 + i >= d) continue;
+        if (wide) {
+            const float* src = state_at(row0 + i, col0 + c4);
+            if (CPT == 4) {
+                const float4 v = *reinterpret_cast<const float4*>(src);
+                S[i][0] = v.x; S[i][1 % CPT] = v.y; S[i][2 % CPT] = v.z; S[i][3 % CPT] = v.w;
+            } else if (CPT == 2) {
+                const float2 v = *reinterpret_cast<const float2*>(src);
+                S[i][0] = v.x; S[i][1 % CPT] = v.y;
             }
+            continue;
+        }
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) {
+            if (!norm_slice) { if (col0 + c4 + j < a.slices * 32) S[i][j] = *state_at(row0 + i, col0 + c4 + j); }
+            else if (c4 + j == 0) S[i][j] = n_state[row0 + i];
         }
     }
     auto fetch = [&](int c0, int stage) {                // the chunk that starts at row c0, on its way into a stage
@@ -270,12 +285,17 @@ __global__ void __launch_bounds__(SCAN_THREADS) mlstm_scan_kernel(MlstmArgs a, i
     }
 #pragma unroll
     for (int i = 0; i < RT; ++i) {
+        if (row0 + i >= d) continue;
+        if (wide) {
+            float* dst = state_at(row0 + i, col0 + c4);
+            if (CPT == 4) *reinterpret_cast<float4*>(dst) = make_float4(S[i][0], S[i][1 % CPT], S[i][2 % CPT], S[i][3 % CPT]);
+            else if (CPT == 2) *reinterpret_cast<float2*>(dst) = make_float2(S[i][0], S[i][1 % CPT]);
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < CPT; ++j) {
-            if (row0 + i < d) {
-                if (!norm_slice) { if (col0 + c4 + j < a.slices * 32) *state_at(row0 + i, col0 + c4 + j) = S[i][j]; }
-                else if (c4 + j == 0) n_state[row0 + i] = S[i][j];
-            }
+            if (!norm_slice) { if (col0 + c4 + j < a.slices * 32) *state_at(row0 + i, col0 + c4 + j) = S[i][j]; }
+            else if (c4 + j == 0) n_state[row0 + i] = S[i][j];
         }
     }
 }
