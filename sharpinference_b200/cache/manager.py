@@ -110,7 +110,8 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, schedule: Sequence, blocks: Sequence, *, page_size: int, num_pages, max_requests: int,
-                 dtype: torch.dtype, device="cuda:0", allocate: bool = True):
+                 dtype: torch.dtype, device="cuda:0", allocate: bool = True,
+                 model_state_specs: Optional[Dict[str, StateSpec]] = None):
         """``schedule``/``blocks`` as in :class:`DecoderModel`.  ``num_pages`` is an int (every
         group gets that many) or a dict ``group index -> pages``.  ``allocate=False`` keeps the
         bookkeeping without device tensors (host-only tests)."""
@@ -126,6 +127,12 @@ class CacheManager:
         self._entry_group: Dict[int, Tuple[int, int]] = {}      # schedule index -> (group, index within group)
         self._entry_state: Dict[int, torch.Tensor] = {}
         self._entry_state_spec: Dict[int, StateSpec] = {}
+        # named state: what a block and its mixer declare as ``state_specs`` (name -> StateSpec), per schedule
+        # entry, and what the model declares for itself (``model_state_specs``)
+        self._entry_named_spec: Dict[int, Dict[str, StateSpec]] = {}
+        self._entry_named: Dict[int, Dict[str, torch.Tensor]] = {}
+        self._model_state_spec: Dict[str, StateSpec] = dict(model_state_specs or {})
+        self.model_states: Dict[str, torch.Tensor] = {}
         self.requests: Dict[Hashable, RequestCache] = {}
         self.state_slots = FreeList(max_requests)
         self._schedule = list(schedule)
@@ -149,6 +156,11 @@ class CacheManager:
             sspec = getattr(mixer, "state_spec", None)
             if sspec is not None:
                 self._entry_state_spec[index] = sspec
+            named: Dict[str, StateSpec] = {}
+            for owner in (blocks[entry.layer], mixer):
+                named.update(getattr(owner, "state_specs", None) or {})
+            if named:
+                self._entry_named_spec[index] = named
         for index, entry in enumerate(self._schedule):
             if entry.cache_from is not None:
                 self._entry_group[index] = self._entry_group[entry.cache_from]
@@ -162,6 +174,11 @@ class CacheManager:
             for index, sspec in self._entry_state_spec.items():
                 self._entry_state[index] = torch.zeros((max_requests, *sspec.shape), dtype=sspec.dtype,
                                                        device=self.device)
+            for index, named in self._entry_named_spec.items():
+                self._entry_named[index] = {name: torch.zeros((max_requests, *sp.shape), dtype=sp.dtype,
+                                                              device=self.device) for name, sp in named.items()}
+            self.model_states = {name: torch.zeros((max_requests, *sp.shape), dtype=sp.dtype, device=self.device)
+                                 for name, sp in self._model_state_spec.items()}
 
     # -- what the layers get -------------------------------------------------------------
     def layer_slots(self) -> List[LayerSlot]:
@@ -174,6 +191,7 @@ class CacheManager:
                 slot.kv = self.groups[gi].kv[within] if self.groups[gi].kv is not None else None
                 slot.writes_cache = entry.cache_from is None
             slot.state = self._entry_state.get(index)
+            slot.states = self._entry_named.get(index, {})
             slots.append(slot)
         return slots
 
@@ -185,6 +203,11 @@ class CacheManager:
             raise OutOfSlots(f"all {self.max_requests} state slots are held")
         slot = self.state_slots.take()
         for state in self._entry_state.values():
+            state[slot].zero_()
+        for named in self._entry_named.values():
+            for state in named.values():
+                state[slot].zero_()
+        for state in self.model_states.values():
             state[slot].zero_()
         rc = RequestCache(request_id, slot, tables={g.index: [] for g in self.groups}, version=self._next_version())
         self.requests[request_id] = rc

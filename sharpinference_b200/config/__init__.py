@@ -2,6 +2,8 @@
 from .base import ConfigError, ConfigReader, architecture_name, read_config_json
 from .llama4 import Llama4TextConfig, RopeScaling
 from .notedra import NotedraConfig, NotedraLayer, NotedraMLP
+from .zaposun import ZaposunAttention, ZaposunConfig, ZaposunLayer, ZaposunScan
 
 __all__ = ["ConfigError", "ConfigReader", "architecture_name", "read_config_json",
-           "Llama4TextConfig", "RopeScaling", "NotedraConfig", "NotedraLayer", "NotedraMLP"]
+           "Llama4TextConfig", "RopeScaling", "NotedraConfig", "NotedraLayer", "NotedraMLP", "ZaposunAttention",
+           "ZaposunConfig", "ZaposunLayer", "ZaposunScan"]

@@ -407,3 +407,62 @@ SHARPI_API int sharpi_timestamp(unsigned long long* slots, int index, cudaStream
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// act(gate) * up over a fused [M, 2I] gate|up product, and tanh as one more plain activation
+// (sharpi_act_only); a scale applied in place.
+template <typename TO, int ACT>
+__global__ void gated_act_kernel(const float* __restrict__ gate_up, TO* __restrict__ out, int I) {
+    pdl_wait();
+    const size_t m = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= I) return;
+    const float g = gate_up[m * 2 * I + i], u = gate_up[m * 2 * I + I + i];
+    out[m * I + i] = from_float<TO>(activate<ACT>(g) * u);
+}
+
+template <typename TO>
+static int launch_gated_act(const float* gate_up, TO* out, int M, int I, int act, cudaStream_t stream) {
+    const dim3 grid((I + 255) / 256, M);
+    if (act == ACT_RELU2) SHARPI_LAUNCH_PDL((gated_act_kernel<TO, ACT_RELU2>), grid, 256, 0, stream, gate_up, out, I);
+    else if (act == ACT_GELU_TANH) SHARPI_LAUNCH_PDL((gated_act_kernel<TO, ACT_GELU_TANH>), grid, 256, 0, stream, gate_up, out, I);
+    else if (act == ACT_SILU) SHARPI_LAUNCH_PDL((gated_act_kernel<TO, ACT_SILU>), grid, 256, 0, stream, gate_up, out, I);
+    else return SHARPI_BAD_ARGUMENT;
+    return SHARPI_OK;
+}
+
+SHARPI_API int sharpi_gated_act(const float* gate_up, void* out, int out_dtype, int M, int I, int act,
+                                cudaStream_t stream) {
+    if (M <= 0 || I <= 0) return SHARPI_OK;
+    if (out_dtype == SHARPI_F32) return launch_gated_act<float>(gate_up, (float*)out, M, I, act, stream);
+    if (out_dtype == SHARPI_BF16) return launch_gated_act<bf16>(gate_up, (bf16*)out, M, I, act, stream);
+    return SHARPI_BAD_ARGUMENT;
+}
+
+template <typename TO>
+__global__ void tanh_kernel(const float* __restrict__ y, TO* __restrict__ out, long long n) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_float<TO>(tanhf(y[i]));
+}
+
+SHARPI_API int sharpi_tanh(const float* y, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return SHARPI_OK;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_dtype == SHARPI_F32) SHARPI_LAUNCH_PDL(tanh_kernel<float>, blocks, 256, 0, stream, y, (float*)out, n);
+    else if (out_dtype == SHARPI_BF16) SHARPI_LAUNCH_PDL(tanh_kernel<bf16>, blocks, 256, 0, stream, y, (bf16*)out, n);
+    else return SHARPI_BAD_ARGUMENT;
+    return SHARPI_OK;
+}
+
+__global__ void scale_kernel(float* y, float s, long long n) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] *= s;
+}
+
+SHARPI_API int sharpi_scale(float* y, float s, long long n, cudaStream_t stream) {
+    if (n <= 0) return SHARPI_OK;
+    SHARPI_LAUNCH_PDL(scale_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, y, s, n);
+    return SHARPI_OK;
+}

@@ -289,3 +289,157 @@ SHARPI_API int sharpi_qkv_post(const float* qkv, const int* positions, const int
     SHARPI_CHECK_LAUNCH();
     return SHARPI_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// The general form: heads padded to D elements whose keys use the first `dk` and whose values the first `dv`;
+// an RMS norm with a weight on q and k over their dk elements BEFORE the rotation; a rotation of the first
+// `rot` elements of q and k only (pairs (i, i + rot/2) or (2i, 2i+1) within those); and a rotation of every
+// value by its own position over its first `vrot` elements with a frequency table of its own, so that the
+// cache holds rotated values (the head's output is turned back by sharpi_rotate_heads).  One warp a (row, head).
+struct QkvRotArgs {
+    const float* qkv;        // [T, (nq + 2 nkv) * D]
+    const int* positions;
+    const int* row_req;
+    const int* block_table;
+    const float* q_norm_w;   // [dk] or null: no norm on q and k
+    const float* k_norm_w;
+    const float* inv_freq;   // [rot / 2] or null
+    const float* inv_freq_v; // [vrot / 2] or null
+    void* q_out;
+    void* kv_base;
+    int T, nq, nkv, D, dk, dv, rot, vrot;
+    int max_blocks, page_size, pairing, write_kv;
+    float eps;
+};
+
+// element i of a head after the rotation of its first `rot` elements by pos * inv_freq[pair]; val(i) gives the
+// element before the rotation
+template <typename F>
+__device__ __forceinline__ float rotated_element(int i, int rot, int pairing, const float* inv_freq, float pos,
+                                                 float sign, F val) {
+    const float own = val(i);
+    if (i >= rot || !inv_freq) return own;
+    const int half = rot >> 1;
+    int pair, other;
+    bool is_first;
+    if (pairing == ROPE_HALVES) {
+        is_first = i < half;
+        pair = is_first ? i : i - half;
+        other = is_first ? i + half : i - half;
+    } else {
+        is_first = (i & 1) == 0;
+        pair = i >> 1;
+        other = is_first ? i + 1 : i - 1;
+    }
+    float sn, cs;
+    sincosf(sign * pos * inv_freq[pair], &sn, &cs);
+    const float o = val(other);
+    return is_first ? own * cs - o * sn : own * cs + o * sn;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256) qkv_post_rot_kernel(QkvRotArgs a) {
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slots = a.nq + 2 * a.nkv;
+    const long long work = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (work >= (long long)a.T * slots) return;
+    const int t = (int)(work / slots), slot = (int)(work % slots);
+    const int D = a.D;
+    const int pos = a.positions[t];
+    const float* src = a.qkv + ((size_t)t * slots + slot) * D;
+    const bool is_q = slot < a.nq;
+    const bool is_k = !is_q && slot < a.nq + a.nkv;
+    TO* dst;
+    if (is_q) {
+        dst = (TO*)a.q_out + ((size_t)t * a.nq + slot) * D;
+    } else {
+        if (!a.write_kv) return;
+        const int head = is_k ? slot - a.nq : slot - a.nq - a.nkv;
+        const int page = a.block_table[(size_t)a.row_req[t] * a.max_blocks + pos / a.page_size];
+        if (page < 0) return;
+        const size_t plane = (size_t)a.nkv * a.page_size * D;
+        dst = (TO*)a.kv_base + ((size_t)page * 2 + (is_k ? 0 : 1)) * plane +
+              ((size_t)head * a.page_size + (pos % a.page_size)) * D;
+    }
+    if (is_q || is_k) {
+        const float* w = is_q ? a.q_norm_w : a.k_norm_w;
+        float scale = 1.0f;
+        if (w) {
+            float ss = 0.0f;
+            for (int i = lane; i < a.dk; i += 32) ss += src[i] * src[i];
+            ss = warp_sum(ss);
+            scale = 1.0f / sqrtf(ss / (float)a.dk + a.eps);
+        }
+        auto val = [&](int i) { return (w && i < a.dk) ? src[i] * scale * w[i] : src[i]; };
+        for (int i = lane; i < D; i += 32)
+            dst[i] = from_float<TO>(rotated_element(i, a.rot, a.pairing, a.inv_freq, (float)pos, 1.0f, val));
+    } else {
+        auto val = [&](int i) { return src[i]; };
+        for (int i = lane; i < D; i += 32)
+            dst[i] = from_float<TO>(rotated_element(i, a.vrot, a.pairing, a.inv_freq_v, (float)pos, 1.0f, val));
+    }
+}
+
+SHARPI_API int sharpi_qkv_post_rot(const float* qkv, const int* positions, const int* row_req, const int* block_table,
+                                   const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq,
+                                   int rot, const float* inv_freq_v, int vrot, int pairing, void* q_out, void* kv_base,
+                                   int out_dtype, int T, int nq, int nkv, int D, int dk, int dv, int max_blocks,
+                                   int page_size, int write_kv, cudaStream_t stream) {
+    if (T <= 0) return SHARPI_OK;
+    if (nq <= 0 || nkv <= 0 || D <= 0 || dk <= 0 || dk > D || dv <= 0 || dv > D || page_size <= 0 || max_blocks <= 0)
+        return SHARPI_BAD_ARGUMENT;
+    if (rot < 0 || (rot & 1) || rot > dk || vrot < 0 || (vrot & 1) || vrot > dv) return SHARPI_BAD_ARGUMENT;
+    if (pairing != ROPE_INTERLEAVED && pairing != ROPE_HALVES) return SHARPI_BAD_ARGUMENT;
+    QkvRotArgs a;
+    a.qkv = qkv; a.positions = positions; a.row_req = row_req; a.block_table = block_table;
+    a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.inv_freq = rot ? inv_freq : nullptr;
+    a.inv_freq_v = vrot ? inv_freq_v : nullptr; a.q_out = q_out; a.kv_base = kv_base;
+    a.T = T; a.nq = nq; a.nkv = nkv; a.D = D; a.dk = dk; a.dv = dv; a.rot = rot; a.vrot = vrot;
+    a.max_blocks = max_blocks; a.page_size = page_size; a.pairing = pairing; a.write_kv = write_kv; a.eps = eps;
+    const long long work = (long long)T * (nq + 2 * nkv);
+    const long long blocks = (work + 7) / 8;
+    if (blocks > 2147483647LL) return SHARPI_BAD_ARGUMENT;
+    if (out_dtype == SHARPI_F32) SHARPI_LAUNCH_PDL(qkv_post_rot_kernel<float>, (unsigned)blocks, 256, 0, stream, a);
+    else if (out_dtype == SHARPI_BF16) SHARPI_LAUNCH_PDL(qkv_post_rot_kernel<bf16>, (unsigned)blocks, 256, 0, stream, a);
+    else return SHARPI_BAD_ARGUMENT;
+    return SHARPI_OK;
+}
+
+// Every head of `in` [T, heads, D] turned by sign * position over its first `rot` elements (the rest copied):
+// the inverse rotation of attention outputs whose values were cached rotated.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+rotate_heads_kernel(const TI* in, const int* positions, const float* __restrict__ inv_freq, TO* out, long long work,
+                    int heads, int D, int rot, int pairing, float sign) {
+    pdl_wait();
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= work) return;
+    const int lane = threadIdx.x & 31;
+    const int t = (int)(item / heads);
+    const TI* src = in + (size_t)item * D;
+    TO* dst = out + (size_t)item * D;
+    const float pos = (float)positions[t];
+    auto val = [&](int i) { return to_float(src[i]); };
+    for (int i = lane; i < D; i += 32)
+        dst[i] = from_float<TO>(rotated_element(i, rot, pairing, inv_freq, pos, sign, val));
+}
+
+SHARPI_API int sharpi_rotate_heads(const void* in, int in_dtype, const int* positions, const float* inv_freq, void* out,
+                                   int out_dtype, int T, int heads, int D, int rot, int pairing, float sign,
+                                   cudaStream_t stream) {
+    if (T <= 0) return SHARPI_OK;
+    if (heads <= 0 || D <= 0 || rot < 0 || (rot & 1) || rot > D) return SHARPI_BAD_ARGUMENT;
+    if (pairing != ROPE_INTERLEAVED && pairing != ROPE_HALVES) return SHARPI_BAD_ARGUMENT;
+    const long long work = (long long)T * heads;
+    const unsigned blocks = (unsigned)((work + 7) / 8);
+#define ROT_CASE(TI, TO)                                                                                         \
+    SHARPI_LAUNCH_PDL((rotate_heads_kernel<TI, TO>), blocks, 256, 0, stream, (const TI*)in, positions, inv_freq, \
+                      (TO*)out, work, heads, D, rot, pairing, sign)
+    if (in_dtype == SHARPI_F32 && out_dtype == SHARPI_F32) ROT_CASE(float, float);
+    else if (in_dtype == SHARPI_BF16 && out_dtype == SHARPI_BF16) ROT_CASE(bf16, bf16);
+    else if (in_dtype == SHARPI_F32 && out_dtype == SHARPI_BF16) ROT_CASE(float, bf16);
+    else return SHARPI_BAD_ARGUMENT;
+#undef ROT_CASE
+    return SHARPI_OK;
+}

@@ -109,7 +109,7 @@ class Engine:
         num_pages = self._size_cache()
         self.cache = CacheManager(self.model.schedule, self.model.blocks, page_size=o.page_size,
                                   num_pages=num_pages, max_requests=o.max_batch, dtype=self.model.act_dtype,
-                                  device=self.device)
+                                  device=self.device, model_state_specs=getattr(self.model, "state_specs", None))
         self.runner = StepRunner(self.model, self.cache)
         self.runner.use_graphs = self.runner.use_graphs and o.cuda_graphs
         self.scheduler = Scheduler(self.cache, max_batch=o.max_batch, max_tokens_per_step=o.max_tokens_per_step)

@@ -103,6 +103,7 @@ class StepRunner:
                                and (getattr(b, "ffn", False) is None or getattr(getattr(b, "ffn", None), "graph_safe", False))
                                for b in model.blocks)
                            and all(getattr(op, "graph_safe", False) for op in getattr(model, "stream_ops", []))
+                           and (getattr(model, "embedder", None) is None or getattr(model.embedder, "graph_safe", False))
                            ) if hasattr(model, "blocks") else False
         self.max_graphs = 32
         self._graphs: Dict[tuple, dict] = {}
@@ -239,6 +240,7 @@ class StepRunner:
             max_context=(max(s + n for s, n in zip(starts, lengths)) if buffers is None
                          else hs.width * self.cache.page_size),
             decode_only=all(n == 1 for n in lengths), plans=plans,
+            model_states=getattr(self.cache, "model_states", {}),
         )
 
     # The word in which a tensor-core kernel records a wait that gave up is copied to pinned host memory

@@ -59,6 +59,20 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_moe_combine": ("moe_topk", [P, P, P, I, I, I, P]),
     "sharpi_mlstm_recurrence": ("mlstm", [P, I, I, I, I, I, I, P, P, P, P, P, LL, I, I, I, I, I, I, F, F, P, P, P, P]),
     "sharpi_mlstm_out": ("mlstm", [P, P, P, P, I, P, F, I, I, I, P, I, P]),
+    "sharpi_embed_pair": ("hyper", [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P]),
+    "sharpi_hc_mix_norm": ("hyper", [P, P, P, P, P, P, P, P, I, I, I, I, I, F, P]),
+    "sharpi_token_shift": ("hyper", [P, P, P, LL, P, P, P, P, I, I, I, I, P]),
+    "sharpi_norm_mean2": ("hyper", [P, P, P, P, P, I, I, F, F, P]),
+    "sharpi_wkv_recurrence": ("wkv", [P, P, P, P, P, P, P, P, P, LL, P, I, I, I, P]),
+    "sharpi_wkv_out": ("wkv", [P, P, P, P, I, I, I, I, F, P]),
+    "sharpi_causal_conv": ("mamba", [P, I, P, P, P, LL, P, P, P, P, P, I, I, I, I, I, P]),
+    "sharpi_slice_cols": ("mamba", [P, I, I, I, P, I, I, P]),
+    "sharpi_selective_scan": ("mamba", [P, P, P, P, I, I, I, P, P, P, I, P, P, P, LL, P, I, I, I, I, P]),
+    "sharpi_qkv_post_rot": ("rope_kv", [P, P, P, P, P, P, F, P, I, P, I, I, P, P, I, I, I, I, I, I, I, I, I, I, P]),
+    "sharpi_rotate_heads": ("rope_kv", [P, I, P, P, P, I, I, I, I, I, I, F, P]),
+    "sharpi_gated_act": ("elementwise", [P, P, I, I, I, I, P]),
+    "sharpi_tanh": ("elementwise", [P, P, I, LL, P]),
+    "sharpi_scale": ("elementwise", [P, F, LL, P]),
 }
 
 _libs: Dict[str, ctypes.CDLL] = {}

@@ -880,3 +880,262 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
                                        top_p.data_ptr(), min_p.data_ptr(), uniform.data_ptr(), probs.data_ptr(),
                                        out.data_ptr(), _stream()), "sharpi_sample_rows")
     return out
+
+
+# ---------------------------------------------------------------------------------------
+# Several residual streams, token shift, hashed pair embedding (hyper.cu)
+HC_MAX_STREAMS = 8
+
+
+def embed_pair(ids: torch.Tensor, embed: torch.Tensor, pairs: torch.Tensor, *, row_request: torch.Tensor,
+               row_offsets: torch.Tensor, state_slots: torch.Tensor, prev_state: torch.Tensor, streams: int,
+               buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """``embed[token] + pairs[(prev * mul_prev + token * mul_cur) mod buckets]`` (row ``buckets`` for a sequence's
+    first token) as float32, written ``streams`` times side by side: ``[T, streams * H]``.  ``prev_state`` int32
+    ``[slots]`` holds every request's last token plus one (0: none yet) and is moved on."""
+    _need(ids, "ids", torch.int32)
+    _need(embed, "embed")
+    _need(pairs, "pairs", embed.dtype)
+    _need(prev_state, "prev_state", torch.int32)
+    for name, t in (("row_request", row_request), ("row_offsets", row_offsets), ("state_slots", state_slots)):
+        _need(t, name, torch.int32)
+    T, (V, H) = ids.numel(), embed.shape
+    if pairs.shape != (buckets + 1, H):
+        raise KernelError(f"pair table is {tuple(pairs.shape)}, expected [{buckets + 1}, {H}]")
+    out = torch.empty((T, streams * H), dtype=torch.float32, device=embed.device)
+    check(kernel("sharpi_embed_pair")(ids.data_ptr(), embed.data_ptr(), pairs.data_ptr(), dtype_code(embed.dtype),
+                                      row_request.data_ptr(), row_offsets.data_ptr(), state_slots.data_ptr(),
+                                      prev_state.data_ptr(), out.data_ptr(), T, H, streams, V, int(buckets),
+                                      int(mul_prev), int(mul_cur), _stream()), "sharpi_embed_pair")
+    return out
+
+
+def hc_mix_norm(x: torch.Tensor, pending, inc: Optional[torch.Tensor], weight: torch.Tensor, *, streams: int,
+                groups: int, eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x`` float32 ``[T, streams * H]``.  With ``pending = (y, mix, out)``: every stream becomes
+    ``x_t <- sum_s mix[s, t] x_s + out[t] y`` (in place; not stored when ``rows`` gathers).  Returns the norm in
+    ``groups`` consecutive parts, times ``weight``, of ``sum_t inc[t] x_t`` (the plain sum when ``inc`` is None)
+    for every row, or for the rows named by ``rows``."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    H = weight.numel()
+    if x.shape[-1] != streams * H:
+        raise KernelError(f"x has rows of {x.shape[-1]}, expected streams * width = {streams * H}")
+    y = mix = outc = None
+    if pending is not None:
+        y, mix, outc = pending
+        _need(y, "y", torch.float32)
+        _need(mix, "mix", torch.float32)
+        _need(outc, "out coefficients", torch.float32)
+        if mix.numel() != streams * streams or outc.numel() != streams or y.shape[-1] != H:
+            raise KernelError("pending update disagrees with the number of streams or the width")
+    if inc is not None:
+        _need(inc, "in coefficients", torch.float32)
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    R = rows.numel() if rows is not None else x.shape[0]
+    h = torch.empty((R, H), dtype=out_dtype, device=x.device)
+    check(kernel("sharpi_hc_mix_norm")(x.data_ptr(), _ptr(y), _ptr(mix), _ptr(outc), _ptr(inc), weight.data_ptr(),
+                                       _ptr(rows), h.data_ptr(), dtype_code(out_dtype), R, H, streams, int(groups),
+                                       float(eps), _stream()), "sharpi_hc_mix_norm")
+    return h
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, *, row_request: torch.Tensor,
+                row_offsets: torch.Tensor, state_slots: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``out[k] = h + (h' - h) * mu[k]`` for the K rows of ``mu`` ``[K, H]``; ``h'`` is the previous row of the same
+    request, or ``state[slot]`` for the first row of a portion; ``state[slot]`` becomes the portion's last ``h``.
+    ``[K, T, H]`` in ``out_dtype``."""
+    _need(h, "h", torch.float32)
+    _need(mu, "mu", torch.float32)
+    _need(state, "state", torch.float32)
+    T, H = h.shape
+    K = mu.numel() // H
+    if mu.numel() != K * H or state.shape[-1] != H:
+        raise KernelError("mu or state disagree with the width")
+    out = torch.empty((K, T, H), dtype=out_dtype, device=h.device)
+    check(kernel("sharpi_token_shift")(h.data_ptr(), mu.data_ptr(), state.data_ptr(), state.stride(0),
+                                       row_request.data_ptr(), row_offsets.data_ptr(), state_slots.data_ptr(),
+                                       out.data_ptr(), dtype_code(out_dtype), T, H, K, _stream()), "sharpi_token_shift")
+    return out
+
+
+def norm_mean2(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, eps: float,
+               scale: float = 0.5) -> torch.Tensor:
+    """``scale * (rms(a) * wa + rms(b) * wb)`` row by row, float32."""
+    for name, t in (("a", a), ("b", b), ("wa", wa), ("wb", wb)):
+        _need(t, name, torch.float32)
+    T, H = a.shape
+    if b.shape != a.shape or wa.numel() != H or wb.numel() != H:
+        raise KernelError("branches and weights disagree on the width")
+    out = torch.empty_like(a)
+    check(kernel("sharpi_norm_mean2")(a.data_ptr(), wa.data_ptr(), b.data_ptr(), wb.data_ptr(), out.data_ptr(), T, H,
+                                      float(eps), float(scale), _stream()), "sharpi_norm_mean2")
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# WKV recurrence (wkv.cu)
+WKV_MAX_HEAD_SIZE = 256
+
+
+def wkv_recurrence(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, wraw: torch.Tensor, w0: torch.Tensor,
+                   u: torch.Tensor, *, row_offsets: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor,
+                   heads: int, d: int) -> torch.Tensor:
+    """``o_t = (S + diag(u) k_t v_t^T)^T r_t``, ``S <- diag(exp(-exp(wraw_t + w0))) S + k_t v_t^T`` per head over
+    the rows of every request, from and into ``state [slots, heads * d * d]``; float32 ``[T, heads * d]``."""
+    for name, t in (("r", r), ("k", k), ("v", v), ("wraw", wraw), ("w0", w0), ("u", u), ("state", state)):
+        _need(t, name, torch.float32)
+    T = r.shape[0]
+    if any(t.shape != (T, heads * d) for t in (r, k, v, wraw)) or w0.numel() != heads * d or u.numel() != heads * d:
+        raise KernelError("r, k, v, the raw decay, w0 and u must all be heads * d wide")
+    if state.shape[-1] != heads * d * d:
+        raise KernelError(f"state is {tuple(state.shape)}, expected [slots, {heads * d * d}]")
+    o = torch.empty((T, heads * d), dtype=torch.float32, device=r.device)
+    check(kernel("sharpi_wkv_recurrence")(r.data_ptr(), k.data_ptr(), v.data_ptr(), wraw.data_ptr(), w0.data_ptr(),
+                                          u.data_ptr(), row_offsets.data_ptr(), state_slots.data_ptr(),
+                                          state.data_ptr(), state.stride(0), o.data_ptr(), state_slots.numel(), heads,
+                                          d, _stream()), "sharpi_wkv_recurrence")
+    return o
+
+
+def wkv_out(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, heads: int, d: int,
+            out_dtype: torch.dtype) -> torch.Tensor:
+    """Every head of ``o`` divided by its root mean square, times ``weight`` and ``silu(gate)``."""
+    _need(o, "o", torch.float32)
+    _need(gate, "gate", torch.float32)
+    _need(weight, "weight", torch.float32)
+    T = o.shape[0]
+    out = torch.empty((T, heads * d), dtype=out_dtype, device=o.device)
+    check(kernel("sharpi_wkv_out")(o.data_ptr(), gate.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                   dtype_code(out_dtype), T, heads, d, float(eps), _stream()), "sharpi_wkv_out")
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# Selective scan and its convolution (mamba.cu)
+SCAN_MAX_STATES = 256
+
+
+def causal_conv(xz: torch.Tensor, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                state: torch.Tensor, *, row_request: torch.Tensor, row_offsets: torch.Tensor,
+                state_slots: torch.Tensor, act_dtype: torch.dtype):
+    """``silu`` of the causal convolution of the first ``channels`` columns of ``xz`` (float32 ``[T, ld]``) with
+    ``weight [channels, taps]`` (last column: the current token) and ``bias``; inputs before a portion come from
+    ``state [slots, (taps - 1) * channels]``, which is moved on.  Returns ``(x32, x_act)``."""
+    _need(xz, "xz", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(state, "state", torch.float32)
+    T, ld = xz.shape
+    taps = weight.numel() // channels
+    if weight.numel() != channels * taps or state.shape[-1] != max(taps - 1, 1) * channels or channels > ld:
+        raise KernelError("convolution weight, state and input disagree on channels or taps")
+    x32 = torch.empty((T, channels), dtype=torch.float32, device=xz.device)
+    xact = x32 if act_dtype == torch.float32 else torch.empty((T, channels), dtype=act_dtype, device=xz.device)
+    check(kernel("sharpi_causal_conv")(xz.data_ptr(), ld, weight.data_ptr(), _ptr(bias), state.data_ptr(),
+                                       state.stride(0), row_request.data_ptr(), row_offsets.data_ptr(),
+                                       state_slots.data_ptr(), x32.data_ptr(),
+                                       None if act_dtype == torch.float32 else xact.data_ptr(), dtype_code(act_dtype),
+                                       T, state_slots.numel(), channels, taps, _stream()), "sharpi_causal_conv")
+    return x32, xact
+
+
+def slice_cols(src: torch.Tensor, col0: int, ncols: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Columns ``col0 .. col0 + ncols - 1`` of a float32 matrix, contiguous, in ``out_dtype``."""
+    _need(src, "src", torch.float32)
+    T, ld = src.shape
+    out = torch.empty((T, ncols), dtype=out_dtype, device=src.device)
+    check(kernel("sharpi_slice_cols")(src.data_ptr(), ld, col0, ncols, out.data_ptr(), dtype_code(out_dtype), T,
+                                      _stream()), "sharpi_slice_cols")
+    return out
+
+
+def selective_scan(x: torch.Tensor, dtraw: torch.Tensor, dt_bias: torch.Tensor, bc: torch.Tensor, col_b: int,
+                   col_c: int, a_log: torch.Tensor, dskip: torch.Tensor, xz: torch.Tensor, col_z: int, *,
+                   row_offsets: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """The selective scan over the rows of every request from and into ``state [slots, channels * states]``;
+    ``(S C + D x) * silu(z)`` in ``out_dtype``, ``z`` being the columns of ``xz`` from ``col_z``."""
+    for name, t in (("x", x), ("dtraw", dtraw), ("dt_bias", dt_bias), ("bc", bc), ("a_log", a_log), ("dskip", dskip),
+                    ("xz", xz), ("state", state)):
+        _need(t, name, torch.float32)
+    T, C = x.shape
+    N = a_log.numel() // C
+    if dtraw.shape != (T, C) or a_log.numel() != C * N or state.shape[-1] != C * N or max(col_b, col_c) + N > bc.shape[1]:
+        raise KernelError("scan inputs disagree on channels or states")
+    if col_z + C > xz.shape[1]:
+        raise KernelError("the gate's columns lie outside the fused projection")
+    out = torch.empty((T, C), dtype=out_dtype, device=x.device)
+    z = xz[:, col_z:]
+    check(kernel("sharpi_selective_scan")(x.data_ptr(), dtraw.data_ptr(), dt_bias.data_ptr(), bc.data_ptr(),
+                                          bc.shape[1], col_b, col_c, a_log.data_ptr(), dskip.data_ptr(), z.data_ptr(),
+                                          xz.shape[1], row_offsets.data_ptr(), state_slots.data_ptr(), state.data_ptr(),
+                                          state.stride(0), out.data_ptr(), dtype_code(out_dtype), state_slots.numel(),
+                                          C, N, _stream()), "sharpi_selective_scan")
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+def qkv_post_rot(qkv: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor,
+                 q_out: torch.Tensor, kv_layer: torch.Tensor, *, nq: int, nkv: int, D: int, key_dim: int,
+                 value_dim: int, page_size: int, pairing: int, q_norm_weight: Optional[torch.Tensor],
+                 k_norm_weight: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int,
+                 inv_freq_v: Optional[torch.Tensor], v_rot_dims: int, write_kv: bool = True) -> None:
+    """The general form of :func:`qkv_post`: weighted RMS norm of q and k before the rotation, rotation of the first
+    ``rot_dims`` elements, values rotated over their first ``v_rot_dims`` elements with ``inv_freq_v``."""
+    _need(qkv, "qkv", torch.float32)
+    T = positions.numel()
+    if qkv.shape != (T, (nq + 2 * nkv) * D):
+        raise KernelError(f"qkv is {tuple(qkv.shape)}, expected [{T}, {(nq + 2 * nkv) * D}]")
+    for name, t in (("q norm weight", q_norm_weight), ("k norm weight", k_norm_weight)):
+        if t is not None:
+            _need(t, name, torch.float32)
+            if t.numel() != key_dim:
+                raise KernelError(f"{name} has {t.numel()} entries, the key size is {key_dim}")
+    if inv_freq is not None and inv_freq.numel() != rot_dims // 2:
+        raise KernelError(f"inv_freq has {inv_freq.numel()} entries, {rot_dims} rotated elements need {rot_dims // 2}")
+    if inv_freq_v is not None and inv_freq_v.numel() != v_rot_dims // 2:
+        raise KernelError(f"the values' inv_freq has {inv_freq_v.numel()} entries, expected {v_rot_dims // 2}")
+    check(kernel("sharpi_qkv_post_rot")(qkv.data_ptr(), positions.data_ptr(), row_req.data_ptr(), block_table.data_ptr(),
+                                        _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), _ptr(inv_freq),
+                                        int(rot_dims if inv_freq is not None else 0), _ptr(inv_freq_v),
+                                        int(v_rot_dims if inv_freq_v is not None else 0), pairing, q_out.data_ptr(),
+                                        kv_layer.data_ptr(), dtype_code(q_out.dtype), T, nq, nkv, D, key_dim, value_dim,
+                                        block_table.shape[-1], page_size, int(write_kv), _stream()),
+          "sharpi_qkv_post_rot")
+
+
+def rotate_heads(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, *, heads: int, D: int,
+                 rot_dims: int, pairing: int, sign: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """Every head of ``x [T, heads * D]`` turned by ``sign * position`` over its first ``rot_dims`` elements."""
+    _need(x, "x")
+    _need(inv_freq, "inv_freq", torch.float32)
+    T = positions.numel()
+    out = torch.empty((T, heads * D), dtype=out_dtype, device=x.device)
+    check(kernel("sharpi_rotate_heads")(x.data_ptr(), dtype_code(x.dtype), positions.data_ptr(), inv_freq.data_ptr(),
+                                        out.data_ptr(), dtype_code(out_dtype), T, heads, D, rot_dims, pairing,
+                                        float(sign), _stream()), "sharpi_rotate_heads")
+    return out
+
+
+def gated_act(gate_up: torch.Tensor, act: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``act(g) * u`` over a fused ``[M, 2I]`` gate|up product (float32 in)."""
+    _need(gate_up, "gate_up", torch.float32)
+    M, I2 = gate_up.shape
+    out = torch.empty((M, I2 // 2), dtype=out_dtype, device=gate_up.device)
+    check(kernel("sharpi_gated_act")(gate_up.data_ptr(), out.data_ptr(), dtype_code(out_dtype), M, I2 // 2, int(act),
+                                     _stream()), "sharpi_gated_act")
+    return out
+
+
+def tanh(y: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    _need(y, "y", torch.float32)
+    out = torch.empty(y.shape, dtype=out_dtype, device=y.device)
+    check(kernel("sharpi_tanh")(y.data_ptr(), out.data_ptr(), dtype_code(out_dtype), y.numel(), _stream()), "sharpi_tanh")
+    return out
+
+
+def scale_(y: torch.Tensor, s: float) -> torch.Tensor:
+    _need(y, "y", torch.float32)
+    check(kernel("sharpi_scale")(y.data_ptr(), float(s), y.numel(), _stream()), "sharpi_scale")
+    return y

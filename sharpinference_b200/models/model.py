@@ -29,7 +29,11 @@ class ScheduleEntry:
 class DecoderModel:
     def __init__(self, *, embedding: torch.Tensor, blocks: Sequence[Block], final_norm: Norm, head: Linear,
                  act_dtype: torch.dtype, schedule: Optional[Sequence[ScheduleEntry]] = None,
-                 eos_token_ids: Sequence[int] = (), config=None, stream_ops: Sequence[StreamOp] = ()):
+                 eos_token_ids: Sequence[int] = (), config=None, stream_ops: Sequence[StreamOp] = (),
+                 embedder=None, logit_scale: float = 1.0):
+        """``embedder``: a part whose ``forward(ctx)`` gives the float32 residual stream(s) of the step's rows
+        in place of the plain table lookup (its ``state_specs`` become per-request state of the model);
+        ``logit_scale`` multiplies the head's output."""
         self.embedding = embedding                  # [V, H]
         self.blocks: List[Block] = list(blocks)
         self.stream_ops: List[StreamOp] = list(stream_ops)
@@ -41,6 +45,9 @@ class DecoderModel:
         self.vocab_size, self.hidden_size = embedding.shape
         self.eos_token_ids = tuple(eos_token_ids)
         self.config = config
+        self.embedder = embedder
+        self.state_specs = dict(getattr(embedder, "state_specs", None) or {})
+        self.logit_scale = float(logit_scale)
         self._validate_schedule()
 
     def set_schedule(self, schedule: Sequence[ScheduleEntry]) -> "DecoderModel":
@@ -71,7 +78,7 @@ class DecoderModel:
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """Run the step's rows through every scheduled block; float32 logits ``[R, V]`` at
         ``ctx.want_rows`` (None if no logits are wanted)."""
-        x = ops.embed_gather(ctx.token_ids, self.embedding)
+        x = self.embedder.forward(ctx) if self.embedder is not None else ops.embed_gather(ctx.token_ids, self.embedding)
         # stream operations read the embedding output; the blocks add into x in place, so it is gathered twice
         x0 = ops.embed_gather(ctx.token_ids, self.embedding) if self.stream_ops else None
         pending = None
@@ -82,7 +89,11 @@ class DecoderModel:
                 x, pending = self.stream_ops[entry.before].forward(ctx, x, pending, x0)
             x, pending = self.blocks[entry.layer].forward(ctx, ctx.slots[index], x, pending)
             if norms is not None or streams is not None:
-                after = x.float() if pending is None else x.float() + pending.float()
+                traced = getattr(self.blocks[entry.layer], "traced_stream", None)
+                if traced is not None:
+                    after = traced(x, pending)
+                else:
+                    after = x.float() if pending is None else x.float() + pending.float()
                 if norms is not None:
                     norms.append(after.square().sum(dim=1).sqrt())
                 if streams is not None:
@@ -90,4 +101,5 @@ class DecoderModel:
         if ctx.want_rows is None or ctx.want_rows.numel() == 0:
             return None
         h, _ = self.final_norm.apply(x, pending, rows=ctx.want_rows, out_dtype=self.act_dtype)
-        return self.head(h)
+        logits = self.head(h)
+        return ops.scale_(logits, self.logit_scale) if self.logit_scale != 1.0 else logits

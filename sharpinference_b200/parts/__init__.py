@@ -3,15 +3,20 @@ from .base import (Block, CacheSpec, FeedForward, LayerSlot, Mixer, Norm, Part, 
                    StepContext, StreamOp, make_part, part_kinds, register_part)
 from .linear import GroupedLinear, Linear
 from .norm import L2Norm, RMSNorm
-from .position import NoPositionEncoding, RotaryEncoding, partial_rotary_inv_freq, rotary_inv_freq
+from .position import (NoPositionEncoding, RotaryEncoding, leading_rotary_inv_freq, partial_rotary_inv_freq,
+                       rotary_inv_freq)
 from .attention import PagedAttention
 from .mlstm import MLSTMMixer, fused_mlstm_columns
 from .feedforward import DenseMLP, DenseSwiGLU, MoESigmoidTop1, MoESigmoidTopK
 from .block import ParallelBlock, PreNormBlock
 from .stream import ReinjectInput
+from .hyper import GroupRMSNorm, HyperBlock, PairEmbedding
+from .wkv import WKVMixer
+from .mamba import BranchPair, SelectiveScanMixer
 
 __all__ = ["Block", "CacheSpec", "FeedForward", "LayerSlot", "Mixer", "Norm", "Part", "PositionEncoding",
            "StateSpec", "StepContext", "make_part", "part_kinds", "register_part", "GroupedLinear", "Linear",
            "L2Norm", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "rotary_inv_freq", "PagedAttention",
            "DenseSwiGLU", "MoESigmoidTop1", "PreNormBlock", "StreamOp", "partial_rotary_inv_freq", "MLSTMMixer",
-           "fused_mlstm_columns", "DenseMLP", "MoESigmoidTopK", "ParallelBlock", "ReinjectInput"]
+           "fused_mlstm_columns", "DenseMLP", "MoESigmoidTopK", "ParallelBlock", "ReinjectInput", "GroupRMSNorm",
+           "HyperBlock", "PairEmbedding", "WKVMixer", "BranchPair", "SelectiveScanMixer", "leading_rotary_inv_freq"]

@@ -106,13 +106,21 @@ class PagedAttention(Mixer):
                  qk_norm: Optional[Norm] = None, qk_norm_first: bool = False,
                  temperature: Optional[Tuple[float, float]] = None,
                  softmax_scale: Optional[float] = None, act_dtype: torch.dtype = torch.bfloat16,
-                 value_dim: Optional[int] = None):
+                 value_dim: Optional[int] = None, value_position: Optional[PositionEncoding] = None,
+                 k_norm: Optional[Norm] = None):
         """``qk_norm``: any :class:`Norm` over the head size, applied to every head of q and k; after the
         position encoding (Llama 4's order) unless ``qk_norm_first``.  The weightless L2 norm after a rotation
         runs inside the kernel that rotates and writes the cache; every other combination applies the norm as
         a launch of its own on q and on k.  ``value_dim``: the size of a value head when it is not ``head_dim``
         (``qkv`` then has ``heads * head_dim + kv_heads * (head_dim + value_dim)`` rows and ``out`` reads
-        ``heads * value_dim`` columns)."""
+        ``heads * value_dim`` columns).
+
+        ``value_position``: a rotary encoding by which every value is turned by its own position before it is
+        cached; each head's output (the weighted sum of the values) is turned back by the query's position.
+        ``k_norm``: the norm of k when it is not the one of q (``qk_norm``).  A rotation of only the leading
+        elements of a head (``RotaryEncoding(rot_dims=...)``), rotated values, and a weighted norm before the
+        rotation together with unequal key and value sizes run in the general form of the fused kernel
+        (``sharpi_qkv_post_rot``): norm first (``qk_norm_first``), then the rotation, then the cache write."""
         if num_heads % num_kv_heads != 0:
             raise ValueError(f"heads ({num_heads}) must be a multiple of kv heads ({num_kv_heads})")
         key_dim = head_dim
@@ -126,7 +134,33 @@ class PagedAttention(Mixer):
         if out.in_features != num_heads * value_dim:
             raise ValueError(f"output projection reads {out.in_features} columns, expected {num_heads * value_dim}")
         self.key_dim, self.value_dim = key_dim, value_dim
-        if value_dim != key_dim:
+        self.value_position, self.k_norm = value_position, (k_norm if k_norm is not None else qk_norm)
+        rot = position.rotary() if position is not None else None
+        self._general = (value_position is not None or getattr(position, "rot_dims", None) is not None
+                         or (value_dim != key_dim and (qk_norm_first or (rot is not None and rot[1] == "halves"))))
+        if self._general:
+            if position is not None and rot is None:
+                raise ValueError("the general fused kernel takes rotary (or no) position encodings only")
+            if qk_norm is not None and not qk_norm_first:
+                raise ValueError("the general fused kernel norms q and k before the rotation (qk_norm_first=True)")
+            if value_position is not None and value_position.rotary() is None:
+                raise ValueError("values can only be turned by a rotary encoding")
+            if value_position is not None and rot is not None and value_position.rotary()[1] != rot[1]:
+                raise ValueError("keys and values must pair their elements the same way")
+            self._rot_dims = 0 if rot is None else (position.rot_dims if position.rot_dims is not None else key_dim)
+            self._v_rot_dims = 0
+            if value_position is not None:
+                vd = getattr(value_position, "rot_dims", None)
+                self._v_rot_dims = vd if vd is not None else value_dim
+                if self._v_rot_dims > value_dim:
+                    raise ValueError(f"{self._v_rot_dims} rotated value elements exceed the value size {value_dim}")
+            if self._rot_dims > key_dim:
+                raise ValueError(f"{self._rot_dims} rotated elements exceed the key size {key_dim}")
+            if value_dim != key_dim:
+                head_dim = max(key_dim, value_dim)
+                head_dim = (head_dim + 15) // 16 * 16 if head_dim <= 128 else head_dim + (head_dim & 1)
+                qkv, out = _pad_projections(qkv, out, num_heads, num_kv_heads, key_dim, value_dim, head_dim)
+        elif value_dim != key_dim:
             head_dim = max(key_dim, value_dim)
             head_dim = (head_dim + 15) // 16 * 16 if head_dim <= 128 else head_dim + (head_dim & 1)
             if qk_norm is not None and not (getattr(qk_norm, "fuses_into_rotation", False) and not qk_norm_first):
@@ -150,8 +184,9 @@ class PagedAttention(Mixer):
         self.qk_norm_first = bool(qk_norm_first)
         rotary = position is not None and position.rotary() is not None
         # the fused kernel's order is rotation, weightless norm, temperature
-        self._norm_fused = (qk_norm is not None and not qk_norm_first
+        self._norm_fused = (qk_norm is not None and not qk_norm_first and not self._general
                             and getattr(qk_norm, "fuses_into_rotation", False))
+        self._ones = None
         if qk_norm is not None and not self._norm_fused and not qk_norm_first and rotary:
             raise ValueError(f"a q/k norm of kind '{qk_norm.kind}' after a rotary encoding is not built (only the "
                              f"weightless L2 norm fuses into the rotation kernel): place it before the position "
@@ -185,6 +220,8 @@ class PagedAttention(Mixer):
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         table = ctx.block_tables[slot.group]
         qkv = self.qkv(h)                                                       # [T, (nq + 2 nkv) d] float32
+        if self._general:
+            return self._forward_general(ctx, slot, plan, table, qkv)
 
         rot = self.position.rotary() if self.position is not None else None
         if self.position is not None and rot is None and type(self.position).apply is not PositionEncoding.apply:
@@ -207,6 +244,41 @@ class PagedAttention(Mixer):
                      l2_eps=self.qk_norm.eps if self._norm_fused else -1.0,
                      temp_attn_scale=attn_scale, temp_floor_scale=floor_scale, write_kv=slot.writes_cache,
                      l2_count=self.key_dim)
+        return self.out(self._attend(ctx, slot, plan, table, q))
+
+    def _norm_weight(self, norm: Optional[Norm], device) -> Optional[torch.Tensor]:
+        if norm is None:
+            return None
+        w = getattr(norm, "weight", None)
+        if w is None:                       # a weightless norm: the kernel multiplies by ones
+            if self._ones is None:
+                self._ones = torch.ones(self.key_dim, dtype=torch.float32, device=device)
+            w = self._ones
+        return w
+
+    def _forward_general(self, ctx: StepContext, slot: LayerSlot, plan, table, qkv: torch.Tensor) -> torch.Tensor:
+        T, nq, nkv, d = ctx.num_tokens, self.num_heads, self.num_kv_heads, self.head_dim
+        rot = self.position.rotary() if self.position is not None else None
+        vrot = self.value_position.rotary() if self.value_position is not None else None
+        pairing = _PAIRING_CODE[(rot or vrot or (None, "halves"))[1]]
+        q = torch.empty((T, nq, d), dtype=self.act_dtype, device=qkv.device)
+        ops.qkv_post_rot(qkv, ctx.positions, ctx.row_request, table, q, slot.kv, nq=nq, nkv=nkv, D=d,
+                         key_dim=self.key_dim, value_dim=self.value_dim, page_size=slot.page_size, pairing=pairing,
+                         q_norm_weight=self._norm_weight(self.qk_norm, qkv.device),
+                         k_norm_weight=self._norm_weight(self.k_norm, qkv.device),
+                         eps=self.qk_norm.eps if self.qk_norm is not None else 0.0,
+                         inv_freq=rot[0] if rot is not None else None, rot_dims=self._rot_dims,
+                         inv_freq_v=vrot[0] if vrot is not None else None, v_rot_dims=self._v_rot_dims,
+                         write_kv=slot.writes_cache)
+        o = self._attend(ctx, slot, plan, table, q)
+        if vrot is not None:                # every head's sum of rotated values, turned back by the row's position
+            o = ops.rotate_heads(o, ctx.positions, vrot[0], heads=nq, D=d, rot_dims=self._v_rot_dims, pairing=pairing,
+                                 sign=-1.0, out_dtype=self.act_dtype)
+        return self.out(o)
+
+    def _attend(self, ctx: StepContext, slot: LayerSlot, plan, table, q: torch.Tensor) -> torch.Tensor:
+        T, nq, nkv, d = ctx.num_tokens, self.num_heads, self.num_kv_heads, self.head_dim
+        h = q
         mask_kind, mask_span = _MASK_CODE[self.cache_spec.kind], max(self.cache_spec.span, 1)
         if self.act_dtype == torch.bfloat16 and d in ops.FAST_ATTENTION_HEAD_SIZES:
             # tensor-core kernels: tiles of prompt rows, and single rows split over their keys
@@ -224,4 +296,4 @@ class PagedAttention(Mixer):
             o = ops.paged_attention_generic(q, slot.kv, table, ctx.row_request, ctx.positions, nq=nq, nkv=nkv, d=d,
                                             page_size=slot.page_size, mask_kind=mask_kind, mask_span=mask_span,
                                             scale=self.softmax_scale)
-        return self.out(o)
+        return o

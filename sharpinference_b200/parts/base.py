@@ -84,6 +84,8 @@ class LayerSlot:
     writes_cache: bool = True               # False: reads the cache that another entry writes
     state: Optional[torch.Tensor] = None    # [state_slots, *StateSpec.shape]
     page_size: int = 0
+    # named per-request state of the block and its mixer (``state_specs``): name -> [state_slots, *shape]
+    states: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
 @dataclass
@@ -112,6 +114,8 @@ class StepContext:
     # (None where an array is empty) and the host-side values, as attributes (see StepPlanner)
     plans: Dict[Hashable, SimpleNamespace] = field(default_factory=dict)
     extras: Dict[str, Any] = field(default_factory=dict)
+    # per-request state that belongs to the model and to no layer (``DecoderModel.state_specs``)
+    model_states: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
 # ---------------------------------------------------------------------------------------
@@ -178,6 +182,10 @@ class PositionEncoding(Part):
 class Mixer(Part):
     cache_spec: Optional[CacheSpec] = None
     state_spec: Optional[StateSpec] = None
+    # further per-request state by name (``slot.states[name]``); a block may declare ``state_specs`` too
+    state_specs: Optional[Dict[str, StateSpec]] = None
+    # True: ``h`` arrives as the unrounded float32 activations instead of the activation dtype
+    wants_fp32_input: bool = False
 
     def step_planner(self, page_size: int) -> Optional[StepPlanner]:
         """The planner of this mixer's per-step metadata, or None if the step context is all it needs."""

@@ -25,14 +25,20 @@ from .linear import GroupedLinear, Linear
 @register_part("feed_forward", "dense_swiglu")
 class DenseSwiGLU(FeedForward):
     graph_safe = True        # reads the step through device tensors only: may be captured in a CUDA graph
-    def __init__(self, *, gate_up: Linear, down: Linear, act_dtype: torch.dtype = torch.bfloat16):
+    def __init__(self, *, gate_up: Linear, down: Linear, act_dtype: torch.dtype = torch.bfloat16,
+                 activation: str = "silu"):
+        """``activation``: what is applied to the gate half, ``silu`` (SwiGLU), ``gelu_tanh`` or ``relu2``."""
         if gate_up.out_features != 2 * down.in_features:
             raise ValueError(f"fused gate|up weight has {gate_up.out_features} rows, expected 2 * {down.in_features}")
-        self.gate_up, self.down, self.act_dtype = gate_up, down, act_dtype
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation '{activation}' is not one of {', '.join(sorted(ops.ACTIVATIONS))}")
+        self.gate_up, self.down, self.act_dtype, self.activation = gate_up, down, act_dtype, activation
 
     def forward(self, ctx: StepContext, h: torch.Tensor, h32: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
-        if self.act_dtype == torch.bfloat16 and self.gate_up.streams(h) and self.gate_up.bias is None:
+        if self.activation != "silu":
+            act = ops.gated_act(self.gate_up(h), ops.ACTIVATIONS[self.activation], self.act_dtype)
+        elif self.act_dtype == torch.bfloat16 and self.gate_up.streams(h) and self.gate_up.bias is None:
             act = ops.dense_rows(h, self.gate_up.weight, swiglu=True)     # SwiGLU in the product's epilogue
         else:
             act = ops.swiglu(self.gate_up(h), self.act_dtype)

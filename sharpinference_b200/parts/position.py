@@ -70,13 +70,28 @@ def partial_rotary_inv_freq(head_dim: int, rot_dims: int, base: float) -> torch.
     return out.to(torch.float32)
 
 
+def leading_rotary_inv_freq(rot_dims: int, base: float) -> torch.Tensor:
+    """float32 ``[rot_dims / 2]``: ``base^(-2i / rot_dims)``, formed in float64 and rounded once (the table of a
+    :class:`RotaryEncoding` with ``rot_dims``)."""
+    if rot_dims % 2 or rot_dims < 0:
+        raise ValueError(f"rotated size {rot_dims} must be even and not negative")
+    i = torch.arange(rot_dims // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / float(max(rot_dims, 1))).to(torch.float32)
+
+
 @register_part("position", "rotary")
 class RotaryEncoding(PositionEncoding):
-    def __init__(self, inv_freq: torch.Tensor, pairing: str = "interleaved"):
+    def __init__(self, inv_freq: torch.Tensor, pairing: str = "interleaved", rot_dims: Optional[int] = None):
+        """``rot_dims``: only the first ``rot_dims`` elements of a head are turned, paired among themselves
+        (``halves``: ``(i, i + rot_dims / 2)``; ``interleaved``: ``(2i, 2i + 1)``), and ``inv_freq`` has
+        ``rot_dims / 2`` entries; None: the whole head, ``inv_freq`` of half the head size."""
         if pairing not in ("interleaved", "halves"):
             raise ValueError(f"rotary pairing '{pairing}' is not one of interleaved, halves")
+        if rot_dims is not None and (rot_dims % 2 or inv_freq.numel() != rot_dims // 2):
+            raise ValueError(f"{rot_dims} rotated elements need {rot_dims // 2} frequencies, found {inv_freq.numel()}")
         self.inv_freq = inv_freq
         self.pairing = pairing
+        self.rot_dims = rot_dims
 
     def rotary(self) -> Optional[Tuple[torch.Tensor, str]]:
         return self.inv_freq, self.pairing

@@ -68,6 +68,11 @@ class WeightSource:
         declaration): the builder then takes its first layout."""
         return None
 
+    def shape_of(self, name: str) -> Optional[Tuple[int, ...]]:
+        """The shape under which a folder holds ``name``, for the few sizes that no configuration key gives (an
+        inner rank, say); None where there is no folder or no such tensor."""
+        return None
+
 
 class DeclaringWeights(WeightSource):
     """Hands out shape-only tensors and remembers what was asked for."""
@@ -81,7 +86,14 @@ class DeclaringWeights(WeightSource):
         self._optional_present = optional_present
         # the names a folder holds, when the declaration is made to check that folder
         self._stored = None if stored_names is None else set(stored_names)
+        self._stored_shapes = dict(stored_names) if isinstance(stored_names, dict) else {}
         self._prefixes = tuple(prefixes)
+
+    def shape_of(self, name):
+        for pre in self._prefixes:
+            if pre + name in self._stored_shapes:
+                return tuple(self._stored_shapes[pre + name])
+        return None
 
     def stored(self, name):
         if self._stored is None:
@@ -123,6 +135,10 @@ class FileWeights(WeightSource):
 
     def stored(self, name):
         return self.prefix + name in self.entries
+
+    def shape_of(self, name):
+        entry = self.entries.get(self.prefix + name)
+        return None if entry is None else tuple(entry.shape)
 
     # -- checking ----------------------------------------------------------------------
     def choose_prefix(self, decls: Sequence[TensorDecl], candidates=("", "language_model.")) -> str:
