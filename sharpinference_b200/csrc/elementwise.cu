@@ -414,8 +414,8 @@ SHARPI_API int sharpi_timestamp(unsigned long long* slots, int index, cudaStream
 template <typename TO, int ACT>
 __global__ void gated_act_kernel(const float* __restrict__ gate_up, TO* __restrict__ out, int I) {
     pdl_wait();
-    const size_t m = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t m = blockIdx.x;
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
     if (i >= I) return;
     const float g = gate_up[m * 2 * I + i], u = gate_up[m * 2 * I + I + i];
     out[m * I + i] = from_float<TO>(activate<ACT>(g) * u);
@@ -423,7 +423,7 @@ __global__ void gated_act_kernel(const float* __restrict__ gate_up, TO* __restri
 
 template <typename TO>
 static int launch_gated_act(const float* gate_up, TO* out, int M, int I, int act, cudaStream_t stream) {
-    const dim3 grid((I + 255) / 256, M);
+    const dim3 grid(M, (I + 255) / 256);
     if (act == ACT_RELU2) SHARPI_LAUNCH_PDL((gated_act_kernel<TO, ACT_RELU2>), grid, 256, 0, stream, gate_up, out, I);
     else if (act == ACT_GELU_TANH) SHARPI_LAUNCH_PDL((gated_act_kernel<TO, ACT_GELU_TANH>), grid, 256, 0, stream, gate_up, out, I);
     else if (act == ACT_SILU) SHARPI_LAUNCH_PDL((gated_act_kernel<TO, ACT_SILU>), grid, 256, 0, stream, gate_up, out, I);

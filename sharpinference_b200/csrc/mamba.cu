@@ -23,8 +23,8 @@ causal_conv_kernel(const float* in, int ld, const float* __restrict__ w, const f
                    const float* state, long long state_stride, const int* row_request, const int* row_offsets,
                    const int* state_slots, float* x32, TO* xact, int C, int taps) {
     pdl_wait();
-    const int t = blockIdx.y;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
     const int b = row_request[t];
     const int i = t - row_offsets[b];                 // place within the portion
@@ -60,7 +60,7 @@ SHARPI_API int sharpi_causal_conv(const float* in, int ld, const float* w, const
                                   int taps, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (C <= 0 || taps <= 0 || B <= 0) return SHARPI_BAD_ARGUMENT;
-    const dim3 grid((C + 255) / 256, T);
+    const dim3 grid(T, (C + 255) / 256);
     if (act_dtype == SHARPI_F32)
         SHARPI_LAUNCH_PDL(causal_conv_kernel<float>, grid, 256, 0, stream, in, ld, w, bias, (const float*)state,
                           state_stride, row_request, row_offsets, state_slots, x32, (float*)nullptr, C, taps);

@@ -78,7 +78,7 @@ def rotate(x, positions, base, dims, layout, sign=1.0):
     return out
 
 
-def chunk_attention(h, W, p, m, eps, layout="halves", shift_window=0):
+def chunk_attention(h, W, p, m, eps, layout="halves", chunk_delta=0):
     """The left branch of a 'parallel' mixer: grouped-query attention inside chunks of ``mask.size`` positions,
     q/k norm before a partial rotation, values rotated by their position and the head's sum turned back."""
     T = h.shape[0]
@@ -94,11 +94,11 @@ def chunk_attention(h, W, p, m, eps, layout="halves", shift_window=0):
     k = rotate(k, pos, rot["base"], rot["dims"], layout)
     v = rotate(v, pos, rot["base"], dv, layout)
     size = (m.get("mask") or {}).get("size", 0)
+    if size:
+        size += chunk_delta                     # tests: what a chunk one position longer or shorter would give
     out = torch.zeros(T, nq, dv, dtype=F64)
     for i in range(T):
         lo = (i // size) * size if size else 0
-        lo += shift_window
-        lo = max(lo, 0)
         for hq in range(nq):
             g = hq // (nq // nkv)
             s = (k[lo:i + 1, g] @ q[i, hq]) * m["scale"]
@@ -132,8 +132,8 @@ def selective_scan(h, W, p, m):
     return (y * silu(z)) @ W[p + "o"].T
 
 
-def parallel_mixer(h, W, p, m, eps, layout="halves"):
-    left = chunk_attention(h, W, p + "left.", m["left"], eps, layout)
+def parallel_mixer(h, W, p, m, eps, layout="halves", chunk_delta=0):
+    left = chunk_attention(h, W, p + "left.", m["left"], eps, layout, chunk_delta)
     right = selective_scan(h, W, p + "right.", m["right"])
     return 0.5 * (rms(left, eps) * W[p + "left.out"] + rms(right, eps) * W[p + "right.out"])
 
@@ -164,10 +164,31 @@ def gated_mlp(h, W, p):
     return (gelu_tanh(h @ W[p + "gate"].T) * (h @ W[p + "up"].T)) @ W[p + "down"].T
 
 
-def forward(config, W, tokens, *, layout="halves", want_layers=False):
+def load_folder(model_dir):
+    import json
+    import os
+
+    from safetensors.torch import load_file
+    with open(os.path.join(model_dir, "config.json")) as fh:
+        cfg = json.load(fh)
+    w = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in
+         load_file(os.path.join(model_dir, "model.safetensors")).items()}
+    return cfg, w
+
+
+def generate_greedy(config, W, prompt, n):
+    toks, out = list(prompt), []
+    for _ in range(n):
+        nxt = int(torch.argmax(forward(config, W, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
+
+
+def forward(config, W, tokens, *, want_layers=False, chunk_delta=0):
     """Logits [T, vocab] of one whole sequence (and the sum of the streams after every layer)."""
     W = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in W.items()}
-    eps, groups, S = config["norm"]["eps"], config["norm"]["groups"], config["streams"]
+    eps, groups, S = config["norm"]["eps"], config["norm"].get("groups", 1), config.get("streams", 1)
     bg = config["embedding"]["bigram"]
     x0 = embedding(list(tokens), W["embed"], W["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
     xs = [x0.clone() for _ in range(S)]
@@ -185,11 +206,12 @@ def forward(config, W, tokens, *, layout="halves", want_layers=False):
                 if layer["type"] == "wkv":
                     y = wkv_mixer(h, W, p + "mix.", layer["mixer"], eps)
                 else:
-                    y = parallel_mixer(h, W, p + "mix.", layer["mixer"], eps, layout)
+                    layout = (layer["mixer"]["left"].get("rot") or {}).get("layout", "halves")
+                    y = parallel_mixer(h, W, p + "mix.", layer["mixer"], eps, layout, chunk_delta)
             else:
                 y = gated_mlp(h, W, p + "mlp.")
             xs = [sum(W[hc + "mix"][s, t] * xs[s] for s in range(S)) + W[hc + "out"][t] * y for t in range(S)]
         after.append(sum(xs))
     x = group_norm(sum(xs), W["final.norm"], groups, eps)
-    logits = (x @ W["head"].T) * config["logit_scale"]
+    logits = (x @ W["head"].T) * config.get("logit_scale", 1.0)
     return (logits, after) if want_layers else logits
