@@ -8,6 +8,9 @@
     python bench_kernels.py mlstm --batch 64 --tokens 1            (decode: the state streams through once)
     python bench_kernels.py mlstm --batch 1 --tokens 2048          (a prompt portion: float32 FMA work)
     python bench_kernels.py router_topk --tokens 2048 --experts 16 --top 2
+    python bench_kernels.py wkv --batch 64 --tokens 1              (decode; --batch 1 --tokens 2048: a prompt)
+    python bench_kernels.py scan --batch 64 --tokens 1             (convolution and selective scan)
+    python bench_kernels.py streams --tokens 2048                  (stream update + grouped norm, token shift)
     python bench_kernels.py mixture_glue --tokens 2048             (activation, pair rows, combine)
 
 Each run warms the kernel up, times ``--iters`` launches with CUDA events and prints one line with
@@ -189,6 +192,79 @@ def mlstm(ns) -> None:
     flops = 4.0 * T * heads * d * dv
     print(f"mlstm batch={B} tokens={n} heads={heads} d={d} dv={dv}: {ms * 1e3:.1f} us, state {state_bytes / ms / 1e6:.0f} GB/s "
           f"(read and written once), {flops / ms / 1e9:.2f} TFLOP/s float32")
+
+
+def wkv(ns) -> None:
+    """The WKV recurrence and its output kernel for `batch` requests of `tokens` rows each.  Decode (tokens = 1)
+    streams the state once (read and written); a prompt portion is float32 FMA work, 4 d d flops a row and head."""
+    B, n, heads, d = ns.batch, ns.tokens, ns.heads, ns.head_dim
+    T, hd = B * n, heads * d
+    r, k, v, wraw, g = (0.5 * torch.randn(T, hd, device=DEV) for _ in range(5))
+    w0, u, nw = torch.full((hd,), -3.0, device=DEV), torch.randn(hd, device=DEV), torch.ones(hd, device=DEV)
+    per_request = heads * d * d
+    copies = max(1, (300 << 20) // (B * per_request * 4) + 1) if n == 1 else 1
+    state = torch.zeros(copies * B, per_request, device=DEV)
+    offs = torch.arange(0, T + 1, n, dtype=torch.int32, device=DEV)
+    slot_sets = [torch.arange(c * B, (c + 1) * B, dtype=torch.int32, device=DEV) for c in range(copies)]
+    it = {"i": 0}
+
+    def fn():
+        slots = slot_sets[it["i"] % copies]
+        it["i"] += 1
+        o = ops.wkv_recurrence(r, k, v, wraw, w0, u, row_offsets=offs, state_slots=slots, state=state, heads=heads, d=d)
+        ops.wkv_out(o, g, nw, 1e-5, heads, d, torch.bfloat16)
+    ms = _time(fn, max(ns.iters, copies))
+    print(f"wkv batch={B} tokens={n} heads={heads} d={d}: {ms * 1e3:.1f} us, state {2 * B * per_request * 4 / ms / 1e6:.0f} GB/s "
+          f"(read and written once), {4.0 * T * heads * d * d / ms / 1e9:.2f} TFLOP/s float32")
+
+
+def scan(ns) -> None:
+    """The causal convolution and the selective scan for `batch` requests of `tokens` rows each: per row, channel
+    and state one exponential and four flops; decode streams the state once."""
+    B, n, C, N, R = ns.batch, ns.tokens, ns.channels, ns.states, ns.dt_rank
+    T = B * n
+    xz, dbc, dtraw = torch.randn(T, 2 * C, device=DEV), 0.5 * torch.randn(T, R + 2 * N, device=DEV), torch.randn(T, C, device=DEV)
+    conv_w, conv_b = 0.5 * torch.randn(C, ns.taps, device=DEV), torch.zeros(C, device=DEV)
+    dt_b, a_log, dsk = torch.zeros(C, device=DEV), torch.zeros(C, N, device=DEV), torch.ones(C, device=DEV)
+    copies = max(1, (300 << 20) // (B * C * N * 4) + 1) if n == 1 else 1
+    state = torch.zeros(copies * B, C * N, device=DEV)
+    conv_state = torch.zeros(copies * B, max(ns.taps - 1, 1) * C, device=DEV)
+    offs = torch.arange(0, T + 1, n, dtype=torch.int32, device=DEV)
+    rr = torch.arange(T, dtype=torch.int32, device=DEV) // n
+    slot_sets = [torch.arange(c * B, (c + 1) * B, dtype=torch.int32, device=DEV) for c in range(copies)]
+    it = {"i": 0}
+
+    def fn():
+        slots = slot_sets[it["i"] % copies]
+        it["i"] += 1
+        x32, _ = ops.causal_conv(xz, C, conv_w, conv_b, conv_state, row_request=rr, row_offsets=offs, state_slots=slots,
+                                 act_dtype=torch.bfloat16)
+        ops.selective_scan(x32, dtraw, dt_b, dbc, R, R + N, a_log, dsk, xz, C, row_offsets=offs, state_slots=slots,
+                           state=state, out_dtype=torch.bfloat16)
+    ms = _time(fn, max(ns.iters, copies))
+    print(f"scan batch={B} tokens={n} channels={C} states={N}: {ms * 1e3:.1f} us, state {2 * B * C * N * 4 / ms / 1e6:.0f} GB/s "
+          f"(read and written once), {T * C * N / ms / 1e6:.1f} G state updates/s (an exponential and four flops each)")
+
+
+def streams(ns) -> None:
+    """The stream update fused with the grouped norm, and the token shift, over `tokens` rows of `streams` streams:
+    the streams are read and written once (2 S H floats a row), the sublayer output read once."""
+    T, H, S = ns.tokens, ns.hidden, ns.streams
+    x, y = torch.randn(T, S * H, device=DEV), torch.randn(T, H, device=DEV)
+    mix, outc, inc = torch.eye(S, device=DEV).contiguous(), torch.ones(S, device=DEV), torch.full((S,), 1.0 / S, device=DEV)
+    w, mu = torch.ones(H, device=DEV), torch.rand(1, H, device=DEV)
+    state = torch.zeros(1, H, device=DEV)
+    rr = torch.zeros(T, dtype=torch.int32, device=DEV)
+    offs = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    slots = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ms = _time(lambda: ops.hc_mix_norm(x, (y, mix, outc), inc, w, streams=S, groups=ns.groups, eps=1e-6,
+                                       out_dtype=torch.bfloat16), ns.iters)
+    print(f"stream update + norm tokens={T} width={H} streams={S}: {ms * 1e3:.1f} us, "
+          f"{T * H * (8 * S + 4 + 2) / ms / 1e6:.0f} GB/s")
+    h = torch.randn(T, H, device=DEV)
+    ms = _time(lambda: ops.token_shift(h, mu, state, row_request=rr, row_offsets=offs, state_slots=slots,
+                                       out_dtype=torch.bfloat16), ns.iters)
+    print(f"token shift tokens={T} width={H}: {ms * 1e3:.1f} us, {T * H * 6 / ms / 1e6:.0f} GB/s")
 
 
 def router_topk(ns) -> None:
@@ -381,6 +457,26 @@ def main(argv=None) -> int:
     p.add_argument("--key-dim", type=int, default=128)
     p.add_argument("--value-dim", type=int, default=256)
     p.set_defaults(fn=mlstm)
+    p = sub.add_parser("wkv")
+    p.add_argument("--batch", type=int, default=64)
+    p.add_argument("--tokens", type=int, default=1)
+    p.add_argument("--heads", type=int, default=32)
+    p.add_argument("--head-dim", type=int, default=64)
+    p.set_defaults(fn=wkv)
+    p = sub.add_parser("scan")
+    p.add_argument("--batch", type=int, default=64)
+    p.add_argument("--tokens", type=int, default=1)
+    p.add_argument("--channels", type=int, default=4096)
+    p.add_argument("--states", type=int, default=16)
+    p.add_argument("--dt-rank", type=int, default=128)
+    p.add_argument("--taps", type=int, default=4)
+    p.set_defaults(fn=scan)
+    p = sub.add_parser("streams")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--hidden", type=int, default=2048)
+    p.add_argument("--streams", type=int, default=4)
+    p.add_argument("--groups", type=int, default=4)
+    p.set_defaults(fn=streams)
     for name, fn in (("router_topk", router_topk), ("mixture_glue", mixture_glue)):
         p = sub.add_parser(name)
         p.add_argument("--tokens", type=int, default=2048)
