@@ -219,8 +219,9 @@ def wkv(ns) -> None:
 
 
 def scan(ns) -> None:
-    """The causal convolution and the selective scan for `batch` requests of `tokens` rows each: per row, channel
-    and state one exponential and four flops; decode streams the state once."""
+    """The causal convolution (with the gate's silu), the softplus of the step sizes and the selective scan for `batch`
+    requests of `tokens` rows each: per row, channel and state one exponential and four flops; decode streams the
+    state once."""
     B, n, C, N, R = ns.batch, ns.tokens, ns.channels, ns.states, ns.dt_rank
     T = B * n
     xz, dbc, dtraw = torch.randn(T, 2 * C, device=DEV), 0.5 * torch.randn(T, R + 2 * N, device=DEV), torch.randn(T, C, device=DEV)
@@ -233,13 +234,15 @@ def scan(ns) -> None:
     rr = torch.arange(T, dtype=torch.int32, device=DEV) // n
     slot_sets = [torch.arange(c * B, (c + 1) * B, dtype=torch.int32, device=DEV) for c in range(copies)]
     it = {"i": 0}
+    dtwork = torch.empty_like(dtraw)
 
     def fn():
         slots = slot_sets[it["i"] % copies]
         it["i"] += 1
         x32, _ = ops.causal_conv(xz, C, conv_w, conv_b, conv_state, row_request=rr, row_offsets=offs, state_slots=slots,
-                                 act_dtype=torch.bfloat16)
-        ops.selective_scan(x32, dtraw, dt_b, dbc, R, R + N, a_log, dsk, xz, C, row_offsets=offs, state_slots=slots,
+                                 act_dtype=torch.bfloat16, gate_col=C)
+        dt = ops.bias_act(dtraw, dt_b, ops.ACT_SOFTPLUS, torch.float32, out=dtwork)
+        ops.selective_scan(x32, dt, dbc, R, R + N, a_log, dsk, xz, C, row_offsets=offs, state_slots=slots,
                            state=state, out_dtype=torch.bfloat16)
     ms = _time(fn, max(ns.iters, copies))
     print(f"scan batch={B} tokens={n} channels={C} states={N}: {ms * 1e3:.1f} us, state {2 * B * C * N * 4 / ms / 1e6:.0f} GB/s "

@@ -330,12 +330,14 @@ SHARPI_API int sharpi_add_bias(float* y, const float* bias, int M, int N, cudaSt
 //   ACT_RELU2      max(z, 0)^2
 //   ACT_GELU_TANH  0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 //   ACT_SILU       z / (1 + exp(-z))
+//   ACT_SOFTPLUS   log(1 + exp(z))
 // ---------------------------------------------------------------------------------------
-enum SharpiAct : int { ACT_RELU2 = 0, ACT_GELU_TANH = 1, ACT_SILU = 2 };
+enum SharpiAct : int { ACT_RELU2 = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_SOFTPLUS = 3 };
 
 template <int ACT> __device__ __forceinline__ float activate(float z) {
     if (ACT == ACT_RELU2) { const float r = fmaxf(z, 0.0f); return r * r; }
     if (ACT == ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (ACT == ACT_SOFTPLUS) return z > 20.0f ? z : log1pf(expf(z));
     return z / (1.0f + expf(-z));
 }
 
@@ -358,6 +360,7 @@ static int launch_bias_act(const float* y, const float* bias, TO* out, int M, in
     if (act == ACT_RELU2) SHARPI_LAUNCH_PDL((bias_act_kernel<TO, ACT_RELU2>), grid, 256, 0, stream, y, bias, out, N);
     else if (act == ACT_GELU_TANH) SHARPI_LAUNCH_PDL((bias_act_kernel<TO, ACT_GELU_TANH>), grid, 256, 0, stream, y, bias, out, N);
     else if (act == ACT_SILU) SHARPI_LAUNCH_PDL((bias_act_kernel<TO, ACT_SILU>), grid, 256, 0, stream, y, bias, out, N);
+    else if (act == ACT_SOFTPLUS) SHARPI_LAUNCH_PDL((bias_act_kernel<TO, ACT_SOFTPLUS>), grid, 256, 0, stream, y, bias, out, N);
     else return SHARPI_BAD_ARGUMENT;
     return SHARPI_OK;
 }

@@ -132,14 +132,14 @@ def add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) ->
     return out
 
 
-ACT_RELU2, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
-ACTIVATIONS = {"relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU}
+ACT_RELU2, ACT_GELU_TANH, ACT_SILU, ACT_SOFTPLUS = 0, 1, 2, 3
+ACTIVATIONS = {"relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU, "softplus": ACT_SOFTPLUS}
 
 
 def bias_act(y: torch.Tensor, bias: Optional[torch.Tensor], act: int, out_dtype: torch.dtype,
              out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``act(y + bias)`` over a float32 product ``[M, N]`` (``bias`` float32 ``[N]`` or None), in ``out_dtype``:
-    the square of relu, tanh-GELU or SiLU."""
+    the square of relu, tanh-GELU, SiLU or softplus.  ``out`` may be ``y`` itself."""
     _need(y, "y", torch.float32)
     M, N = y.shape
     if bias is not None:
@@ -983,7 +983,8 @@ def wkv_recurrence(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, wraw: torc
                    u: torch.Tensor, *, row_offsets: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor,
                    heads: int, d: int) -> torch.Tensor:
     """``o_t = (S + diag(u) k_t v_t^T)^T r_t``, ``S <- diag(exp(-exp(wraw_t + w0))) S + k_t v_t^T`` per head over
-    the rows of every request, from and into ``state [slots, heads * d * d]``; float32 ``[T, heads * d]``."""
+    the rows of every request, from and into ``state [slots, heads * d * d]``; float32 ``[T, heads * d]``.
+    ``wraw`` is overwritten (with the decay, for heads of up to 128 elements)."""
     for name, t in (("r", r), ("k", k), ("v", v), ("wraw", wraw), ("w0", w0), ("u", u), ("state", state)):
         _need(t, name, torch.float32)
     T = r.shape[0]
@@ -992,10 +993,11 @@ def wkv_recurrence(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, wraw: torc
     if state.shape[-1] != heads * d * d:
         raise KernelError(f"state is {tuple(state.shape)}, expected [slots, {heads * d * d}]")
     o = torch.empty((T, heads * d), dtype=torch.float32, device=r.device)
+    bonus = torch.empty((T, heads), dtype=torch.float32, device=r.device)
     check(kernel("sharpi_wkv_recurrence")(r.data_ptr(), k.data_ptr(), v.data_ptr(), wraw.data_ptr(), w0.data_ptr(),
                                           u.data_ptr(), row_offsets.data_ptr(), state_slots.data_ptr(),
-                                          state.data_ptr(), state.stride(0), o.data_ptr(), state_slots.numel(), heads,
-                                          d, _stream()), "sharpi_wkv_recurrence")
+                                          state.data_ptr(), state.stride(0), o.data_ptr(), bonus.data_ptr(), T,
+                                          state_slots.numel(), heads, d, _stream()), "sharpi_wkv_recurrence")
     return o
 
 
@@ -1019,10 +1021,11 @@ SCAN_MAX_STATES = 256
 
 def causal_conv(xz: torch.Tensor, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
                 state: torch.Tensor, *, row_request: torch.Tensor, row_offsets: torch.Tensor,
-                state_slots: torch.Tensor, act_dtype: torch.dtype):
+                state_slots: torch.Tensor, act_dtype: torch.dtype, gate_col: int = -1):
     """``silu`` of the causal convolution of the first ``channels`` columns of ``xz`` (float32 ``[T, ld]``) with
     ``weight [channels, taps]`` (last column: the current token) and ``bias``; inputs before a portion come from
-    ``state [slots, (taps - 1) * channels]``, which is moved on.  Returns ``(x32, x_act)``."""
+    ``state [slots, (taps - 1) * channels]``, which is moved on.  Returns ``(x32, x_act)``.  With ``gate_col`` the
+    columns ``gate_col .. gate_col + channels - 1`` of ``xz`` are replaced by their ``silu`` in the same pass."""
     _need(xz, "xz", torch.float32)
     _need(weight, "weight", torch.float32)
     _need(state, "state", torch.float32)
@@ -1036,7 +1039,8 @@ def causal_conv(xz: torch.Tensor, channels: int, weight: torch.Tensor, bias: Opt
                                        state.stride(0), row_request.data_ptr(), row_offsets.data_ptr(),
                                        state_slots.data_ptr(), x32.data_ptr(),
                                        None if act_dtype == torch.float32 else xact.data_ptr(), dtype_code(act_dtype),
-                                       T, state_slots.numel(), channels, taps, _stream()), "sharpi_causal_conv")
+                                       T, state_slots.numel(), channels, taps, int(gate_col), _stream()),
+          "sharpi_causal_conv")
     return x32, xact
 
 
@@ -1050,13 +1054,15 @@ def slice_cols(src: torch.Tensor, col0: int, ncols: int, out_dtype: torch.dtype)
     return out
 
 
-def selective_scan(x: torch.Tensor, dtraw: torch.Tensor, dt_bias: torch.Tensor, bc: torch.Tensor, col_b: int,
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, col_b: int,
                    col_c: int, a_log: torch.Tensor, dskip: torch.Tensor, xz: torch.Tensor, col_z: int, *,
                    row_offsets: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor,
                    out_dtype: torch.dtype) -> torch.Tensor:
-    """The selective scan over the rows of every request from and into ``state [slots, channels * states]``;
-    ``(S C + D x) * silu(z)`` in ``out_dtype``, ``z`` being the columns of ``xz`` from ``col_z``."""
-    for name, t in (("x", x), ("dtraw", dtraw), ("dt_bias", dt_bias), ("bc", bc), ("a_log", a_log), ("dskip", dskip),
+    """The selective scan over the rows of every request from and into ``state [slots, channels * states]``:
+    ``(S C + D x) * g`` in ``out_dtype``, with ``dt`` the step sizes themselves (after their softplus) and ``g`` the
+    gate (already ``silu(z)``) in the columns of ``xz`` from ``col_z``."""
+    dtraw = dt
+    for name, t in (("x", x), ("dt", dt), ("bc", bc), ("a_log", a_log), ("dskip", dskip),
                     ("xz", xz), ("state", state)):
         _need(t, name, torch.float32)
     T, C = x.shape
@@ -1067,10 +1073,10 @@ def selective_scan(x: torch.Tensor, dtraw: torch.Tensor, dt_bias: torch.Tensor, 
         raise KernelError("the gate's columns lie outside the fused projection")
     out = torch.empty((T, C), dtype=out_dtype, device=x.device)
     z = xz[:, col_z:]
-    check(kernel("sharpi_selective_scan")(x.data_ptr(), dtraw.data_ptr(), dt_bias.data_ptr(), bc.data_ptr(),
+    check(kernel("sharpi_selective_scan")(x.data_ptr(), dtraw.data_ptr(), None, bc.data_ptr(),
                                           bc.shape[1], col_b, col_c, a_log.data_ptr(), dskip.data_ptr(), z.data_ptr(),
                                           xz.shape[1], row_offsets.data_ptr(), state_slots.data_ptr(), state.data_ptr(),
-                                          state.stride(0), out.data_ptr(), dtype_code(out_dtype), state_slots.numel(),
+                                          state.stride(0), out.data_ptr(), dtype_code(out_dtype), T, state_slots.numel(),
                                           C, N, _stream()), "sharpi_selective_scan")
     return out
 

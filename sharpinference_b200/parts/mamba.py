@@ -55,10 +55,11 @@ class SelectiveScanMixer(Mixer):
         xz = self.in_proj(h)                                                     # [T, 2 inner] float32
         x32, xact = ops.causal_conv(xz, self.inner, self.conv_weight, self.conv_bias, slot.states["conv"],
                                     row_request=ctx.row_request, row_offsets=ctx.row_offsets,
-                                    state_slots=ctx.state_slots, act_dtype=self.act_dtype)
+                                    state_slots=ctx.state_slots, act_dtype=self.act_dtype, gate_col=self.inner)
         dbc = self.x_proj(xact)                                                  # [T, dt_rank + 2 states] float32
-        dtraw = self.dt_proj(ops.slice_cols(dbc, 0, self.dt_rank, self.act_dtype))
-        y = ops.selective_scan(x32, dtraw, self.dt_bias, dbc, self.dt_rank, self.dt_rank + self.states, self.a_log,
+        dt = self.dt_proj(ops.slice_cols(dbc, 0, self.dt_rank, self.act_dtype))
+        ops.bias_act(dt, self.dt_bias, ops.ACT_SOFTPLUS, torch.float32, out=dt)  # the step sizes, in place
+        y = ops.selective_scan(x32, dt, dbc, self.dt_rank, self.dt_rank + self.states, self.a_log,
                                self.d_skip, xz, self.inner, row_offsets=ctx.row_offsets, state_slots=ctx.state_slots,
                                state=slot.states["S"], out_dtype=self.act_dtype)
         return self.out(y)

@@ -243,8 +243,9 @@ def test_convolution_and_selective_scan_kernels(C, N, R, taps):
         rr, off, sl = _step_meta([cut[b] for b in live], [[1, 2][b] for b in live])
         cat = {k: f(torch.cat([data[b][k][at[b]:at[b] + cut[b]] for b in live])) for k in data[0]}
         x32, xact = ops.causal_conv(cat["xz"], C, f(conv_w), f(conv_b), conv_state, row_request=rr, row_offsets=off,
-                                    state_slots=sl, act_dtype=torch.float32)
-        y = ops.selective_scan(x32, cat["dtraw"], f(dt_b), cat["dbc"], R, R + N, f(a_log), f(dsk), cat["xz"], C,
+                                    state_slots=sl, act_dtype=torch.float32, gate_col=C)      # the gate's silu in place
+        dt = ops.bias_act(cat["dtraw"], f(dt_b), ops.ACT_SOFTPLUS, torch.float32, out=cat["dtraw"])
+        y = ops.selective_scan(x32, dt, cat["dbc"], R, R + N, f(a_log), f(dsk), cat["xz"], C,
                                row_offsets=off, state_slots=sl, state=scan_state, out_dtype=torch.float32)
         sliced = ops.slice_cols(cat["dbc"], 0, R, torch.float32)
         assert torch.equal(sliced, cat["dbc"][:, :R].contiguous())
