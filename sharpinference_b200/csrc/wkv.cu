@@ -202,8 +202,9 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(WkvScanArgs a) {
     int buf = 0;
     for (int t0 = first; t0 < end; t0 += CH, buf ^= 1) {
         const int rows = min(CH, end - t0);
-        if (t0 + CH < end) { fetch(t0 + CH, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-        __syncthreads();          // this chunk has arrived; the other buffer and the parts have been read
+        cp_async_wait<0>();
+        __syncthreads();          // this chunk has arrived; the other buffer and the parts have been read by everyone
+        if (t0 + CH < end) fetch(t0 + CH, buf ^ 1);      // arrives while this chunk is walked
         const float* st = stage + buf * CH * 3 * DKP + k0;
         const float* vs = v_s + buf * CH * DVP + j0;
         if (kg < KG) {

@@ -8,7 +8,7 @@ import torch
 
 import plain_zaposun as plain
 import traces
-from zaposun_models import CASE_P, CASE_Q, CASE_R, CASE_S, CASE_T, CASES, write
+from zaposun_models import CASE_P, CASE_Q, CASE_R, CASE_S, CASE_T, CASE_U, CASE_V, CASES, write
 
 from sharpinference_b200.config import ConfigError, ZaposunConfig
 from sharpinference_b200.registry import get_architecture, resolve
@@ -18,7 +18,7 @@ F64 = torch.float64
 
 
 # -- configuration -------------------------------------------------------------------------
-@pytest.mark.parametrize("case", [CASE_P, CASE_Q, CASE_R, CASE_S, CASE_T])
+@pytest.mark.parametrize("case", [CASE_P, CASE_Q, CASE_R, CASE_S, CASE_T, CASE_U, CASE_V])
 def test_config_round_trip(case):
     arch, cfg = resolve(copy.deepcopy(case), "test")
     assert arch.name == "Zaposun" and isinstance(cfg, ZaposunConfig)
@@ -114,6 +114,18 @@ def test_state_of_blocks_mixers_and_the_model_in_the_cache_manager():
     assert b.state_slot == a.state_slot
     assert all(float(t[b.state_slot].abs().sum()) == 0 for t in slots[1].states.values())
     assert int(cache.model_states["prev_token"][b.state_slot]) == 0
+
+
+def test_cache_groups_of_models_with_one_kind_of_mixer():
+    from sharpinference_b200.cache import CacheManager
+    from sharpinference_b200.weights.source import DeclaringWeights
+    arch = get_architecture("Zaposun")
+    for case, kinds in ((CASE_U, []), (CASE_V, [("chunk", 9, 2), ("full", 0, 1)])):
+        _, cfg = resolve(copy.deepcopy(case), "test")
+        model = arch.build(cfg, DeclaringWeights(torch.float32))
+        cache = CacheManager(model.schedule, model.blocks, page_size=4, num_pages=8, max_requests=2, dtype=torch.float32,
+                             device="cpu", model_state_specs=model.state_specs)
+        assert [(g.spec.kind, g.spec.span, len(g.entries)) for g in cache.groups] == kinds
 
 
 # -- the plain implementation against itself ---------------------------------------------------

@@ -15,7 +15,7 @@ DEV = "cuda:0"
 # Relative to the largest |logit| of a request.
 TOL = {"float32": 5e-5, "bfloat16": 4e-2}
 LENGTHS = {"P": [1, 9, 40, 83, 150, 2], "Q": [150, 5, 67, 200, 31], "R": [3, 70, 12, 45, 100, 64, 65],
-           "S": [1, 2, 30, 5], "T": [140, 66, 3, 129]}
+           "S": [1, 2, 30, 5], "T": [140, 66, 3, 129], "U": [33, 1, 80], "V": [70, 5, 41, 100]}
 
 
 def requests_for(name):

@@ -89,9 +89,18 @@ CASE_T = _top(50, 128, 4, 4, 1e-5, 1.0, (301, 7, 11), [
     _par(_left(1, 1, 256, 32, 0.05, 100, rot=(256, 1000.0)), _right(8, 200, 2, 3), 0),
 ])
 
+# U: wkv layers only (no keys or values anywhere: a model without a cache group); V: parallel layers only, two of
+# them with equal attention sizes (one cache group of two entries) and one that sees every earlier position.
+CASE_U = _top(40, 32, 2, 1, 1e-5, 1.0, (11, 5, 3), [_wkv(2, 16, 4, 24), _wkv(1, 32, 2, 0)])
+CASE_V = _top(45, 48, 2, 3, 1e-5, 0.5, (19, 2, 9), [
+    _par(_left(2, 1, 16, 16, 0.7, 9, rot=(16, 30.0)), _right(24, 8, 2, 3), 32),
+    _par(_left(2, 1, 16, 16, 0.7, 9, rot=(16, 30.0)), _right(16, 4, 3, 2), 0),
+    _par({"heads": 3, "kv_heads": 3, "dim": 8, "vdim": 8, "scale": 0.9}, _right(16, 12, 2, 4), 16),
+])
+
 # config, std of the weights, seed
 CASES = {"P": (CASE_P, 0.12, 21), "Q": (CASE_Q, 0.1, 22), "R": (CASE_R, 0.15, 23), "S": (CASE_S, 0.4, 24),
-         "T": (CASE_T, 0.08, 25)}
+         "T": (CASE_T, 0.08, 25), "U": (CASE_U, 0.2, 26), "V": (CASE_V, 0.15, 27)}
 
 
 def write(name: str, out_dir: str) -> str:
