@@ -40,7 +40,7 @@ def _wkv(c: ZaposunConfig, layer: ZaposunLayer, p: str, weights: WeightSource, a
     H, heads, d = c.width, layer.heads, layer.dim
     hd = heads * d
     mu = torch.stack([weights.vector(f"{p}mu.{s}", (H,), init="normal") for s in "rkvgw"]).contiguous()
-    lin = {s: Linear(weights.matrix(p + s, (hd, H)), p + s) for s in "kvg"}
+    lin = {s: weights.matrix(p + s, (hd, H)) for s in "kvg"}
     rank = layer.decay_rank or (weights.shape_of(p + "w1") or (0,))[0]
     if rank <= 0:
         raise ValueError(f"{p}w1: neither the configuration (decay_rank) nor a stored tensor gives the decay's inner size")
@@ -50,9 +50,15 @@ def _wkv(c: ZaposunConfig, layer: ZaposunLayer, p: str, weights: WeightSource, a
     u = weights.vector(p + "u", (heads, d), init="normal")
     norm = weights.vector(p + "norm", (hd,))
     out = Linear(weights.matrix(p + "o", (H, hd)), p + "o")
-    r = Linear(weights.matrix(p + "r", (hd, H)), p + "r")
-    return WKVMixer(mu=mu, r=r, k=lin["k"], v=lin["v"], g=lin["g"], w1=Linear(w1, p + "w1"), w2=w2, w0=w0,
-                    u=u.reshape(-1), head_norm_weight=norm, out=out, heads=heads, head_dim=d, eps=c.eps, act_dtype=act)
+    lin["r"] = weights.matrix(p + "r", (hd, H))
+    stacked = None
+    if weights.device.type != "meta" and len({t.dtype for t in lin.values()}) == 1:
+        stacked = torch.stack([lin[s] for s in "rkvg"]).contiguous()        # the four Linear below are views of it
+        lin = {s: stacked[i] for i, s in enumerate("rkvg")}
+    return WKVMixer(mu=mu, r=Linear(lin["r"], p + "r"), k=Linear(lin["k"], p + "k"), v=Linear(lin["v"], p + "v"),
+                    g=Linear(lin["g"], p + "g"), w1=Linear(w1, p + "w1"), w2=w2, w0=w0, u=u.reshape(-1),
+                    head_norm_weight=norm, out=out, heads=heads, head_dim=d, eps=c.eps, act_dtype=act,
+                    rkvg_weight=stacked)
 
 
 def _attention(c: ZaposunConfig, layer: ZaposunLayer, p: str, weights: WeightSource, act) -> PagedAttention:

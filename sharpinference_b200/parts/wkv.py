@@ -35,10 +35,17 @@ class WKVMixer(Mixer):
     cache_spec = None
     wants_fp32_input = True
 
+    # Steps of up to this many rows compute r, k, v and g (four products of four different inputs) as one grouped
+    # tensor-core product, the four inputs being the groups: one launch instead of four where a step is launch-bound.
+    GROUPED_ROWS = 128
+
     def __init__(self, *, mu: torch.Tensor, r: Linear, k: Linear, v: Linear, g: Linear, w1: Linear, w2: Linear,
                  w0: torch.Tensor, u: torch.Tensor, head_norm_weight: torch.Tensor, out: Linear, heads: int,
-                 head_dim: int, eps: float, act_dtype: torch.dtype = torch.bfloat16):
-        """``mu [5, H]``: the mixing vectors of r, k, v, g, w in this order."""
+                 head_dim: int, eps: float, act_dtype: torch.dtype = torch.bfloat16,
+                 rkvg_weight: torch.Tensor = None):
+        """``mu [5, H]``: the mixing vectors of r, k, v, g, w in this order.  ``rkvg_weight [4, heads * head_dim, H]``:
+        the weights of r, k, v, g stacked (the four ``Linear`` may be views of it), for the grouped product of
+        small steps; None: four products at every size."""
         hd = heads * head_dim
         H = r.in_features
         if head_dim > ops.WKV_MAX_HEAD_SIZE:
@@ -56,13 +63,28 @@ class WKVMixer(Mixer):
         self.mu, self.r, self.k, self.v, self.g, self.w1, self.w2, self.out = mu, r, k, v, g, w1, w2, out
         self.w0, self.u, self.head_norm_weight = w0, u, head_norm_weight
         self.heads, self.head_dim, self.eps, self.act_dtype = heads, head_dim, float(eps), act_dtype
+        self.rkvg_weight = None
+        if (rkvg_weight is not None and rkvg_weight.dtype == torch.bfloat16 and act_dtype == torch.bfloat16
+                and H % 8 == 0 and tuple(rkvg_weight.shape) == (4, hd, H)):
+            self.rkvg_weight = rkvg_weight
+        self._group_offsets = {}
         self.state_specs = {"prev": StateSpec((H,), torch.float32),
                             "S": StateSpec((heads * head_dim * head_dim,), torch.float32)}
 
     def forward(self, ctx: StepContext, slot: LayerSlot, h: torch.Tensor) -> torch.Tensor:
         mixes = ops.token_shift(h, self.mu, slot.states["prev"], row_request=ctx.row_request,
                                 row_offsets=ctx.row_offsets, state_slots=ctx.state_slots, out_dtype=self.act_dtype)
-        r, k, v, g = self.r(mixes[0]), self.k(mixes[1]), self.v(mixes[2]), self.g(mixes[3])
+        T = h.shape[0]
+        if self.rkvg_weight is not None and T <= self.GROUPED_ROWS:
+            offsets = self._group_offsets.get(T)
+            if offsets is None:                      # made on the device, once a step size (the first, eager step)
+                if len(self._group_offsets) > 256:
+                    self._group_offsets.clear()
+                offsets = self._group_offsets[T] = torch.arange(5, dtype=torch.int32, device=h.device) * T
+            r, k, v, g = ops.tc_grouped_gemm(mixes[:4].view(4 * T, -1), self.rkvg_weight, offsets,
+                                             mode=ops.TC_MODE_STORE).view(4, T, -1).unbind(0)
+        else:
+            r, k, v, g = self.r(mixes[0]), self.k(mixes[1]), self.v(mixes[2]), self.g(mixes[3])
         wraw = self.w2(ops.tanh(self.w1(mixes[4]), self.act_dtype))
         o = ops.wkv_recurrence(r, k, v, wraw, self.w0, self.u, row_offsets=ctx.row_offsets,
                                state_slots=ctx.state_slots, state=slot.states["S"], heads=self.heads, d=self.head_dim)
