@@ -1,6 +1,7 @@
 // Several residual streams per token (hyper-connections), the token shift, and the embedding with a hashed
-// pair table.  Everything here is float32 arithmetic; a block serves one row of the step, so a row's result
-// is the same sequence of operations whatever else is in the batch.
+// pair table.  Everything here is float32 arithmetic; a block serves one row of the step (one group of a row in the
+// grouped norm, a tile of a row's columns in the token shift) with a block size that the width alone decides, so a
+// row's result is the same sequence of operations whatever else is in the batch.
 //
 //   sharpi_embed_pair      x = embed[token] + pair[(prev * mul_prev + token * mul_cur) mod buckets], the row
 //                          `buckets` for a sequence's first token; written to every stream.  The previous
@@ -20,7 +21,7 @@
 constexpr int HC_MAX_STREAMS = 8;
 
 template <typename TT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 embed_pair_kernel(const int* ids, const TT* __restrict__ embed, const TT* __restrict__ pairs, const int* row_request,
                   const int* row_offsets, const int* state_slots, int* prev_state, float* out, int H, int S, int V,
                   int buckets, int mul_prev, int mul_cur) {
@@ -61,11 +62,12 @@ SHARPI_API int sharpi_embed_pair(const int* ids, const void* embed, const void* 
                                  int mul_cur, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (H <= 0 || S <= 0 || V <= 0 || buckets <= 0) return SHARPI_BAD_ARGUMENT;
+    const int threads = H >= 1024 ? 1024 : (H + 31) / 32 * 32;
     if (table_dtype == SHARPI_F32)
-        SHARPI_LAUNCH_PDL(embed_pair_kernel<float>, T, 256, 0, stream, ids, (const float*)embed, (const float*)pairs,
+        SHARPI_LAUNCH_PDL(embed_pair_kernel<float>, T, threads, 0, stream, ids, (const float*)embed, (const float*)pairs,
                           row_request, row_offsets, state_slots, prev_state, out, H, S, V, buckets, mul_prev, mul_cur);
     else if (table_dtype == SHARPI_BF16)
-        SHARPI_LAUNCH_PDL(embed_pair_kernel<bf16>, T, 256, 0, stream, ids, (const bf16*)embed, (const bf16*)pairs,
+        SHARPI_LAUNCH_PDL(embed_pair_kernel<bf16>, T, threads, 0, stream, ids, (const bf16*)embed, (const bf16*)pairs,
                           row_request, row_offsets, state_slots, prev_state, out, H, S, V, buckets, mul_prev, mul_cur);
     else
         return SHARPI_BAD_ARGUMENT;
@@ -85,9 +87,12 @@ struct HcArgs {
     float eps;
 };
 
-template <typename TO>
+// PER_GROUP: a block serves one group of one row (small steps: more blocks, one pass); otherwise a block serves a
+// row, group after group.  The block size and the order of every sum are the same either way, so a row's result
+// does not depend on which form ran.
+template <typename TO, bool PER_GROUP>
 __global__ void __launch_bounds__(256) hc_mix_norm_kernel(HcArgs a) {
-    extern __shared__ float u_sm[];              // H floats
+    extern __shared__ float u_sm[];              // the group's columns of u
     __shared__ float red[32];
     __shared__ float coef[HC_MAX_STREAMS * HC_MAX_STREAMS + 2 * HC_MAX_STREAMS];
     pdl_wait();
@@ -95,50 +100,54 @@ __global__ void __launch_bounds__(256) hc_mix_norm_kernel(HcArgs a) {
     float* mix = coef;
     float* outc = coef + HC_MAX_STREAMS * HC_MAX_STREAMS;
     float* inc = outc + HC_MAX_STREAMS;
-    if (threadIdx.x < S * S) mix[threadIdx.x] = a.y ? a.mix[threadIdx.x] : 0.0f;
-    if (threadIdx.x < S) {
-        outc[threadIdx.x] = a.y ? a.outc[threadIdx.x] : 0.0f;
-        inc[threadIdx.x] = a.inc ? a.inc[threadIdx.x] : 1.0f;
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) mix[i] = a.y ? a.mix[i] : 0.0f;
+    for (int i = threadIdx.x; i < S; i += blockDim.x) {
+        outc[i] = a.y ? a.outc[i] : 0.0f;
+        inc[i] = a.inc ? a.inc[i] : 1.0f;
     }
     __syncthreads();
+    // the groups are normed apart, so nothing passes between blocks
     const int r = blockIdx.x;
     const int row = a.rows ? a.rows[r] : r;
-    float* xr = a.x + (size_t)row * S * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float xs[HC_MAX_STREAMS];
-#pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s) xs[s] = s < S ? xr[(size_t)s * H + c] : 0.0f;
-        float u = 0.0f;
-        if (a.y) {
-            const float yv = a.y[(size_t)row * H + c];
-#pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t) {
-                if (t < S) {
-                    float v = 0.0f;
-#pragma unroll
-                    for (int s = 0; s < HC_MAX_STREAMS; ++s)
-                        if (s < S) v += mix[s * S + t] * xs[s];
-                    v += outc[t] * yv;
-                    if (!a.rows) xr[(size_t)t * H + c] = v;
-                    u += inc[t] * v;
-                }
-            }
-        } else {
-#pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t)
-                if (t < S) u += inc[t] * xs[t];
-        }
-        u_sm[c] = u;
-    }
     const int gs = H / a.G;
-    TO* out = (TO*)a.h + (size_t)r * H;
-    for (int g = 0; g < a.G; ++g) {
+    float* xr = a.x + (size_t)row * S * H;
+    const int g_first = PER_GROUP ? blockIdx.y : 0, g_end = PER_GROUP ? blockIdx.y + 1 : a.G;
+    for (int g = g_first; g < g_end; ++g) {
+        const int c0 = g * gs;
         float ss = 0.0f;
-        for (int c = g * gs + threadIdx.x; c < (g + 1) * gs; c += blockDim.x) ss += u_sm[c] * u_sm[c];
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+            const int c = c0 + i;
+            float xs[HC_MAX_STREAMS];
+#pragma unroll
+            for (int s = 0; s < HC_MAX_STREAMS; ++s) xs[s] = s < S ? xr[(size_t)s * H + c] : 0.0f;
+            float u = 0.0f;
+            if (a.y) {
+                const float yv = a.y[(size_t)row * H + c];
+#pragma unroll
+                for (int t = 0; t < HC_MAX_STREAMS; ++t) {
+                    if (t < S) {
+                        float v = 0.0f;
+#pragma unroll
+                        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                            if (s < S) v += mix[s * S + t] * xs[s];
+                        v += outc[t] * yv;
+                        if (!a.rows) xr[(size_t)t * H + c] = v;
+                        u += inc[t] * v;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int t = 0; t < HC_MAX_STREAMS; ++t)
+                    if (t < S) u += inc[t] * xs[t];
+            }
+            u_sm[i] = u;
+            ss += u * u;
+        }
         const float total = block_sum(ss, red);
         const float scale = 1.0f / sqrtf(total / (float)gs + a.eps);
-        for (int c = g * gs + threadIdx.x; c < (g + 1) * gs; c += blockDim.x)
-            out[c] = from_float<TO>(u_sm[c] * scale * a.w[c]);
+        TO* out = (TO*)a.h + (size_t)r * H + c0;
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) out[i] = from_float<TO>(u_sm[i] * scale * a.w[c0 + i]);
+        __syncthreads();          // u_sm is the next group's
     }
 }
 
@@ -147,47 +156,62 @@ SHARPI_API int sharpi_hc_mix_norm(float* x, const float* y, const float* mix, co
                                   float eps, cudaStream_t stream) {
     if (R <= 0) return SHARPI_OK;
     if (H <= 0 || S <= 0 || S > HC_MAX_STREAMS || G <= 0 || H % G != 0) return SHARPI_BAD_ARGUMENT;
-    if ((size_t)H * sizeof(float) > 200 * 1024) return SHARPI_BAD_ARGUMENT;
+    if ((size_t)(H / G) * sizeof(float) > 200 * 1024) return SHARPI_BAD_ARGUMENT;
     HcArgs a;
     a.x = x; a.y = y; a.mix = mix; a.outc = outc; a.inc = inc; a.w = w; a.rows = rows; a.h = h;
     a.H = H; a.S = S; a.G = G; a.eps = eps;
-    const size_t smem = (size_t)H * sizeof(float);
-    if (h_dtype == SHARPI_F32) {
-        if (smem > 48 * 1024 &&
-            cudaFuncSetAttribute(hc_mix_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return SHARPI_LAUNCH_FAILED;
-        SHARPI_LAUNCH_PDL(hc_mix_norm_kernel<float>, R, 256, smem, stream, a);
-    } else if (h_dtype == SHARPI_BF16) {
-        if (smem > 48 * 1024 &&
-            cudaFuncSetAttribute(hc_mix_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return SHARPI_LAUNCH_FAILED;
-        SHARPI_LAUNCH_PDL(hc_mix_norm_kernel<bf16>, R, 256, smem, stream, a);
-    } else {
-        return SHARPI_BAD_ARGUMENT;
-    }
+    const int gs = H / G;
+    const size_t smem = (size_t)gs * sizeof(float);
+    const int threads = gs >= 256 ? 256 : (gs + 31) / 32 * 32;       // the same for both forms
+    const bool per_group = R <= 256;
+#define HC_CASE(TO, PG)                                                                                         \
+    do {                                                                                                        \
+        auto kern = hc_mix_norm_kernel<TO, PG>;                                                                 \
+        if (smem > 48 * 1024 &&                                                                                 \
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)  \
+            return SHARPI_LAUNCH_FAILED;                                                                        \
+        SHARPI_LAUNCH_PDL(kern, dim3(R, PG ? G : 1), threads, smem, stream, a);                                 \
+    } while (0)
+    if (h_dtype == SHARPI_F32) { if (per_group) HC_CASE(float, true); else HC_CASE(float, false); }
+    else if (h_dtype == SHARPI_BF16) { if (per_group) HC_CASE(bf16, true); else HC_CASE(bf16, false); }
+    else return SHARPI_BAD_ARGUMENT;
+#undef HC_CASE
     return SHARPI_OK;
 }
 
-template <typename TO>
+// CPT columns a thread: one in small steps (more blocks), four in large ones (all loads of a thread in flight
+// before its first store).  Element by element the arithmetic is the same.
+template <typename TO, int CPT>
 __global__ void __launch_bounds__(256)
 token_shift_kernel(const float* h, const float* __restrict__ mu, float* state, long long state_stride,
                    const int* row_request, const int* row_offsets, const int* state_slots, TO* out, int T, int H,
                    int K) {
     pdl_wait();
     const int t = blockIdx.x;
+    const int base = blockIdx.y * blockDim.x * CPT + threadIdx.x;
     const int b = row_request[t];
     const int first = row_offsets[b];
     const bool is_first = t == first;
     float* st = state + (size_t)state_slots[b] * state_stride;
     const float* prev = is_first ? st : h + (size_t)(t - 1) * H;
-    const float* cur = h + (size_t)t * H;
     const float* last = h + (size_t)(row_offsets[b + 1] - 1) * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        const float hv = cur[c], pv = prev[c];
-        const float d = pv - hv;
+    float hv[CPT], pv[CPT], lv[CPT];
+#pragma unroll
+    for (int q = 0; q < CPT; ++q) {
+        const int c = base + q * blockDim.x;
+        hv[q] = c < H ? h[(size_t)t * H + c] : 0.0f;
+        pv[q] = c < H ? prev[c] : 0.0f;
+        lv[q] = (is_first && c < H) ? last[c] : 0.0f;
+    }
+#pragma unroll
+    for (int q = 0; q < CPT; ++q) {
+        const int c = base + q * blockDim.x;
+        if (c >= H) continue;
+        const float d = pv[q] - hv[q];
         for (int k = 0; k < K; ++k)
-            out[((size_t)k * T + t) * H + c] = from_float<TO>(hv + d * mu[(size_t)k * H + c]);
-        if (is_first) st[c] = last[c];       // this thread has read st[c]; no other block touches this request's row
+            out[((size_t)k * T + t) * H + c] = from_float<TO>(hv[q] + d * mu[(size_t)k * H + c]);
+        // this thread has read st[c]; no other thread of the launch touches this element of the request's row
+        if (is_first) st[c] = lv[q];
     }
 }
 
@@ -196,18 +220,19 @@ SHARPI_API int sharpi_token_shift(const float* h, const float* mu, float* state,
                                   int out_dtype, int T, int H, int K, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (H <= 0 || K <= 0) return SHARPI_BAD_ARGUMENT;
-    if (out_dtype == SHARPI_F32)
-        SHARPI_LAUNCH_PDL(token_shift_kernel<float>, T, 256, 0, stream, h, mu, state, state_stride, row_request,
-                          row_offsets, state_slots, (float*)out, T, H, K);
-    else if (out_dtype == SHARPI_BF16)
-        SHARPI_LAUNCH_PDL(token_shift_kernel<bf16>, T, 256, 0, stream, h, mu, state, state_stride, row_request,
-                          row_offsets, state_slots, (bf16*)out, T, H, K);
-    else
-        return SHARPI_BAD_ARGUMENT;
+    const bool wide = T >= 512;
+    const dim3 grid(T, (H + (wide ? 1024 : 256) - 1) / (wide ? 1024 : 256));
+#define TS_CASE(TO, CPT)                                                                                       \
+    SHARPI_LAUNCH_PDL((token_shift_kernel<TO, CPT>), grid, 256, 0, stream, h, mu, state, state_stride, row_request, \
+                      row_offsets, state_slots, (TO*)out, T, H, K)
+    if (out_dtype == SHARPI_F32) { if (wide) TS_CASE(float, 4); else TS_CASE(float, 1); }
+    else if (out_dtype == SHARPI_BF16) { if (wide) TS_CASE(bf16, 4); else TS_CASE(bf16, 1); }
+    else return SHARPI_BAD_ARGUMENT;
+#undef TS_CASE
     return SHARPI_OK;
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 norm_mean2_kernel(const float* a, const float* __restrict__ wa, const float* b, const float* __restrict__ wb,
                   float* out, int H, float eps, float scale) {
     __shared__ float red[32];
@@ -230,6 +255,7 @@ SHARPI_API int sharpi_norm_mean2(const float* a, const float* wa, const float* b
                                  int H, float eps, float scale, cudaStream_t stream) {
     if (T <= 0) return SHARPI_OK;
     if (H <= 0) return SHARPI_BAD_ARGUMENT;
-    SHARPI_LAUNCH_PDL(norm_mean2_kernel, T, 256, 0, stream, a, wa, b, wb, out, H, eps, scale);
+    const int threads = H >= 1024 ? 1024 : (H + 31) / 32 * 32;
+    SHARPI_LAUNCH_PDL(norm_mean2_kernel, T, threads, 0, stream, a, wa, b, wb, out, H, eps, scale);
     return SHARPI_OK;
 }
