@@ -110,7 +110,6 @@ SHARPI_API int sharpi_slice_cols(const float* src, int ld, int col0, int ncols, 
 struct ScanArgs {
     const float* x;          // [T, C] after convolution and silu
     const float* dtraw;      // [T, C]: the step sizes (after bias and softplus)
-    const float* dt_bias;    // unused
     const float* bc;         // [T, ld_bc]: B at col_b, C at col_c, N columns each
     int ld_bc, col_b, col_c;
     const float* a_log;      // [C, N]
@@ -306,7 +305,7 @@ static int launch_scan(ScanArgs a, int B, int T, cudaStream_t stream) {
     return SHARPI_OK;
 }
 
-SHARPI_API int sharpi_selective_scan(const float* x, const float* dtraw, const float* dt_bias, const float* bc,
+SHARPI_API int sharpi_selective_scan(const float* x, const float* dtraw, const float* bc,
                                      int ld_bc, int col_b, int col_c, const float* a_log, const float* dskip,
                                      const float* z, int ld_z, const int* row_offsets, const int* state_slots,
                                      float* state, long long state_stride, void* out, int out_dtype, int T, int B,
@@ -314,7 +313,7 @@ SHARPI_API int sharpi_selective_scan(const float* x, const float* dtraw, const f
     if (B <= 0) return SHARPI_OK;
     if (C <= 0 || N <= 0 || N > 256) return SHARPI_BAD_ARGUMENT;
     ScanArgs a;
-    a.x = x; a.dtraw = dtraw; a.dt_bias = dt_bias; a.bc = bc; a.ld_bc = ld_bc; a.col_b = col_b; a.col_c = col_c;
+    a.x = x; a.dtraw = dtraw; a.bc = bc; a.ld_bc = ld_bc; a.col_b = col_b; a.col_c = col_c;
     a.a_log = a_log; a.dskip = dskip; a.z = z; a.ld_z = ld_z; a.row_offsets = row_offsets; a.state_slots = state_slots;
     a.state = state; a.state_stride = state_stride; a.out = out; a.C = C; a.N = N;
     if (out_dtype == SHARPI_F32) return launch_scan<float>(a, B, T, stream);

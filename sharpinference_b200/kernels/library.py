@@ -67,7 +67,7 @@ SIGNATURES: Dict[str, Tuple[str, list]] = {
     "sharpi_wkv_out": ("wkv", [P, P, P, P, I, I, I, I, F, P]),
     "sharpi_causal_conv": ("mamba", [P, I, P, P, P, LL, P, P, P, P, P, I, I, I, I, I, I, P]),
     "sharpi_slice_cols": ("mamba", [P, I, I, I, P, I, I, P]),
-    "sharpi_selective_scan": ("mamba", [P, P, P, P, I, I, I, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, P]),
+    "sharpi_selective_scan": ("mamba", [P, P, P, I, I, I, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, P]),
     "sharpi_qkv_post_rot": ("rope_kv", [P, P, P, P, P, P, F, P, I, P, I, I, P, P, I, I, I, I, I, I, I, I, I, I, P]),
     "sharpi_rotate_heads": ("rope_kv", [P, I, P, P, P, I, I, I, I, I, I, F, P]),
     "sharpi_gated_act": ("elementwise", [P, P, I, I, I, I, P]),

@@ -1061,19 +1061,18 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, col_b: i
     """The selective scan over the rows of every request from and into ``state [slots, channels * states]``:
     ``(S C + D x) * g`` in ``out_dtype``, with ``dt`` the step sizes themselves (after their softplus) and ``g`` the
     gate (already ``silu(z)``) in the columns of ``xz`` from ``col_z``."""
-    dtraw = dt
     for name, t in (("x", x), ("dt", dt), ("bc", bc), ("a_log", a_log), ("dskip", dskip),
                     ("xz", xz), ("state", state)):
         _need(t, name, torch.float32)
     T, C = x.shape
     N = a_log.numel() // C
-    if dtraw.shape != (T, C) or a_log.numel() != C * N or state.shape[-1] != C * N or max(col_b, col_c) + N > bc.shape[1]:
+    if dt.shape != (T, C) or a_log.numel() != C * N or state.shape[-1] != C * N or max(col_b, col_c) + N > bc.shape[1]:
         raise KernelError("scan inputs disagree on channels or states")
     if col_z + C > xz.shape[1]:
         raise KernelError("the gate's columns lie outside the fused projection")
     out = torch.empty((T, C), dtype=out_dtype, device=x.device)
     z = xz[:, col_z:]
-    check(kernel("sharpi_selective_scan")(x.data_ptr(), dtraw.data_ptr(), None, bc.data_ptr(),
+    check(kernel("sharpi_selective_scan")(x.data_ptr(), dt.data_ptr(), bc.data_ptr(),
                                           bc.shape[1], col_b, col_c, a_log.data_ptr(), dskip.data_ptr(), z.data_ptr(),
                                           xz.shape[1], row_offsets.data_ptr(), state_slots.data_ptr(), state.data_ptr(),
                                           state.stride(0), out.data_ptr(), dtype_code(out_dtype), T, state_slots.numel(),

@@ -135,6 +135,31 @@ def test_token_shift_carries_the_previous_row_across_portions():
     assert float(state[3].min()) == 99.0
 
 
+def test_small_and_large_steps_give_the_same_bits():
+    """The stream update with its norm and the token shift have a form for small steps and one for large steps; a
+    row's result is the same bits in both."""
+    from sharpinference_b200.kernels import ops
+    g = torch.Generator().manual_seed(9)
+    S, G, H, T = 3, 4, 4 * 300, 700
+    x = torch.randn(T, S * H, generator=g).to(DEV)
+    y = torch.randn(T, H, generator=g).to(DEV)
+    mix, outc, inc = torch.randn(S, S, generator=g).to(DEV), torch.randn(S, generator=g).to(DEV), torch.randn(S, generator=g).to(DEV)
+    w = torch.randn(H, generator=g).to(DEV)
+    xa, xb = x.clone(), x[:20].clone()
+    big = ops.hc_mix_norm(xa, (y, mix, outc), inc, w, streams=S, groups=G, eps=1e-5, out_dtype=torch.float32)
+    small = ops.hc_mix_norm(xb, (y[:20].contiguous(), mix, outc), inc, w, streams=S, groups=G, eps=1e-5, out_dtype=torch.float32)
+    assert torch.equal(big[:20], small) and torch.equal(xa[:20], xb)
+    h = torch.randn(T, H, generator=g).to(DEV)
+    mu = torch.rand(2, H, generator=g).to(DEV)
+    rr, off, sl = _step_meta([T], [0])
+    st_a, st_b = torch.ones(1, H, device=DEV), torch.ones(1, H, device=DEV)
+    big = ops.token_shift(h, mu, st_a, row_request=rr, row_offsets=off, state_slots=sl, out_dtype=torch.float32)
+    rr, off, sl = _step_meta([20], [0])
+    small = ops.token_shift(h[:20].contiguous(), mu, st_b, row_request=rr, row_offsets=off, state_slots=sl, out_dtype=torch.float32)
+    assert torch.equal(big[:, :20], small)
+    assert torch.equal(st_a[0], h[-1]) and torch.equal(st_b[0], h[19])
+
+
 def test_pair_embedding_uses_the_previous_token_of_the_request():
     from sharpinference_b200.kernels import ops
     g = torch.Generator().manual_seed(6)
