@@ -19,6 +19,14 @@
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
+// 2^x for x <= 0 in one special-function instruction (two units in the last place; results below the smallest
+// normal number become zero, which is what a decay that small is).
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(256)
 causal_conv_kernel(const float* in, int ld, const float* __restrict__ w, const float* __restrict__ bias,
@@ -248,10 +256,10 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(ScanArgs a) {
 #pragma unroll
             for (int i = 0; i < SCAN_NPT / 4; ++i) {
                 const float4 Bv = B4[i], Cv = C4[i];
-                S[4 * i] = fmaf(exp2f(dt * A[4 * i]), S[4 * i], dtx * Bv.x);             acc = fmaf(S[4 * i], Cv.x, acc);
-                S[4 * i + 1] = fmaf(exp2f(dt * A[4 * i + 1]), S[4 * i + 1], dtx * Bv.y); acc = fmaf(S[4 * i + 1], Cv.y, acc);
-                S[4 * i + 2] = fmaf(exp2f(dt * A[4 * i + 2]), S[4 * i + 2], dtx * Bv.z); acc = fmaf(S[4 * i + 2], Cv.z, acc);
-                S[4 * i + 3] = fmaf(exp2f(dt * A[4 * i + 3]), S[4 * i + 3], dtx * Bv.w); acc = fmaf(S[4 * i + 3], Cv.w, acc);
+                S[4 * i] = fmaf(ex2_approx(dt * A[4 * i]), S[4 * i], dtx * Bv.x);             acc = fmaf(S[4 * i], Cv.x, acc);
+                S[4 * i + 1] = fmaf(ex2_approx(dt * A[4 * i + 1]), S[4 * i + 1], dtx * Bv.y); acc = fmaf(S[4 * i + 1], Cv.y, acc);
+                S[4 * i + 2] = fmaf(ex2_approx(dt * A[4 * i + 2]), S[4 * i + 2], dtx * Bv.z); acc = fmaf(S[4 * i + 2], Cv.z, acc);
+                S[4 * i + 3] = fmaf(ex2_approx(dt * A[4 * i + 3]), S[4 * i + 3], dtx * Bv.w); acc = fmaf(S[4 * i + 3], Cv.w, acc);
             }
 #pragma unroll
             for (int o = G >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
