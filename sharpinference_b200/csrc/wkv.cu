@@ -11,7 +11,8 @@
 // exponentials, written over wraw, and the bonus' scalar b_t = sum_i r_t[i] u[i] k_t[i], so that
 // o_t[j] = sum_i r_t[i] S[i][j] + b_t v_t[j].  The walk itself (wkv_scan_kernel) is one block a (request, head): a
 // thread owns a tile of S (eight key channels of four value columns) in registers; r, k, w and v of the next rows
-// arrive in shared memory by cp.async, two chunks of rows in flight.  A request's rows are walked one after the
+// arrive in shared memory by cp.async, two chunks of rows on their way while a third is walked (a chunk of sixteen
+// rows is walked in less time than a chunk takes to arrive).  A request's rows are walked one after the
 // other and a column's parts are added in a fixed order, so a row's result is the same sequence of operations
 // whether it came in a prompt portion or alone.  Heads of more than 128 elements take the form in which
 // a column's key channels are dealt over several threads (wkv_recurrence_kernel).
@@ -114,6 +115,9 @@ wkv_prepare_kernel(const float* r, const float* k, float* wraw, const float* __r
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
 }
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -135,6 +139,7 @@ struct WkvScanArgs {
 };
 
 constexpr int WKV_CH = 16;     // rows a chunk at most
+constexpr int WKV_STAGES = 3;  // chunks in shared memory: one being walked, two on their way
 
 // Thread (kg, jg) keeps KT key channels (kg * KT ...) of CPT value columns (jg * CPT ...) of S in registers.  Per row
 // it adds its part of sum_i r[i] S[i][j] into shared memory and moves its tile of S on; nothing is exchanged between
@@ -150,10 +155,10 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(WkvScanArgs a) {
     const int jg = threadIdx.x % JG, kg = threadIdx.x / JG;
     const int j0 = jg * CPT, k0 = kg * KT;
     const int CH = a.ch;
-    float* stage = sm;                                        // [2][CH][3][DKP]
-    float* v_s = stage + 2 * CH * 3 * DKP;                    // [2][CH][DVP]
-    float* part = v_s + 2 * CH * DVP;                         // [CH][KG][DVP]
-    float* bon = part + CH * KG * DVP;                        // [2][CH]
+    float* stage = sm;                                        // [STAGES][CH][3][DKP]
+    float* v_s = stage + WKV_STAGES * CH * 3 * DKP;           // [STAGES][CH][DVP]
+    float* part = v_s + WKV_STAGES * CH * DVP;                // [CH][KG][DVP]
+    float* bon = part + CH * KG * DVP;                        // [STAGES][CH]
     const int first = a.row_offsets[b], end = a.row_offsets[b + 1];
     const size_t hd = (size_t)a.heads * d, col = (size_t)head * d;
     float* S_g = a.state + (size_t)a.state_slots[b] * a.state_stride + (size_t)head * d * d;
@@ -166,13 +171,13 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(WkvScanArgs a) {
     }
     // keys and columns beyond the head's own stay zero in both buffers
     if (DKP != d)
-        for (int i = threadIdx.x; i < 2 * CH * 3 * DKP; i += blockDim.x)
+        for (int i = threadIdx.x; i < WKV_STAGES * CH * 3 * DKP; i += blockDim.x)
             if (i % DKP >= d) stage[i] = 0.0f;
     if (DVP != d)
-        for (int i = threadIdx.x; i < 2 * CH * DVP; i += blockDim.x)
+        for (int i = threadIdx.x; i < WKV_STAGES * CH * DVP; i += blockDim.x)
             if (i % DVP >= d) v_s[i] = 0.0f;
     auto fetch = [&](int t0, int buf) {
-        const int rows = min(CH, end - t0);
+        const int rows = max(0, min(CH, end - t0));           // none: an empty group keeps the count of groups even
         float* st = stage + buf * CH * 3 * DKP;
         float* vs = v_s + buf * CH * DVP;
         if (a.aligned) {
@@ -195,16 +200,17 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(WkvScanArgs a) {
                 vs[tt * DVP + e] = a.v[g];
             }
         }
-        if (threadIdx.x < rows) bon[buf * CH + threadIdx.x] = a.bonus[(size_t)(t0 + threadIdx.x) * a.heads + head];
+        if (threadIdx.x < rows) cp_async4(bon + buf * CH + threadIdx.x, a.bonus + (size_t)(t0 + threadIdx.x) * a.heads + head);
         cp_async_commit();
     };
-    if (first < end) fetch(first, 0);
+    fetch(first, 0);
+    fetch(first + CH, 1);
     int buf = 0;
-    for (int t0 = first; t0 < end; t0 += CH, buf ^= 1) {
+    for (int t0 = first; t0 < end; t0 += CH, buf = (buf + 1) % WKV_STAGES) {
         const int rows = min(CH, end - t0);
-        cp_async_wait<0>();
-        __syncthreads();          // this chunk has arrived; the other buffer and the parts have been read by everyone
-        if (t0 + CH < end) fetch(t0 + CH, buf ^ 1);      // arrives while this chunk is walked
+        cp_async_wait<1>();       // all but the newest group: this chunk is here, the next may still be on its way
+        __syncthreads();          // ... for everyone; the buffer of the chunk before and the parts have been read
+        fetch(t0 + 2 * CH, (buf + 2) % WKV_STAGES);          // two chunks ahead: a chunk is walked faster than one arrives
         const float* st = stage + buf * CH * 3 * DKP + k0;
         const float* vs = v_s + buf * CH * DVP + j0;
         if (kg < KG) {
@@ -247,11 +253,26 @@ __global__ void __launch_bounds__(MAXT) wkv_scan_kernel(WkvScanArgs a) {
             }
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < rows * d; i += blockDim.x) {
-            const int tt = i / d, j = i % d;
-            float total = 0.0f;
-            for (int g = 0; g < KG; ++g) total += part[(tt * KG + g) * DVP + j];
-            a.o[(size_t)(t0 + tt) * hd + col + j] = fmaf(bon[buf * CH + tt], v_s[(buf * CH + tt) * DVP + j], total);
+        if (CPT == 4) {           // four columns a thread: d is a multiple of four and the rows of o start on 16 bytes
+            for (int i = threadIdx.x; i < rows * JG; i += blockDim.x) {
+                const int tt = i / JG, j = (i % JG) * 4;
+                float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int g = 0; g < KG; ++g) {
+                    const float4 p = *reinterpret_cast<const float4*>(part + (tt * KG + g) * DVP + j);
+                    total.x += p.x; total.y += p.y; total.z += p.z; total.w += p.w;
+                }
+                const float bt = bon[buf * CH + tt];
+                const float4 v4 = *reinterpret_cast<const float4*>(v_s + (buf * CH + tt) * DVP + j);
+                *reinterpret_cast<float4*>(a.o + (size_t)(t0 + tt) * hd + col + j) =
+                    make_float4(fmaf(bt, v4.x, total.x), fmaf(bt, v4.y, total.y), fmaf(bt, v4.z, total.z), fmaf(bt, v4.w, total.w));
+            }
+        } else {
+            for (int i = threadIdx.x; i < rows * d; i += blockDim.x) {
+                const int tt = i / d, j = i % d;
+                float total = 0.0f;
+                for (int g = 0; g < KG; ++g) total += part[(tt * KG + g) * DVP + j];
+                a.o[(size_t)(t0 + tt) * hd + col + j] = fmaf(bon[buf * CH + tt], v_s[(buf * CH + tt) * DVP + j], total);
+            }
         }
     }
 #pragma unroll
@@ -269,7 +290,7 @@ static int launch_wkv_scan(WkvScanArgs a, int B, int T, cudaStream_t stream) {
     const int threads = (KG * JG + 31) / 32 * 32;
     if (threads > MAXT) return SHARPI_BAD_ARGUMENT;
     a.ch = T - B + 1 < WKV_CH ? (T - B + 1 < 1 ? 1 : T - B + 1) : WKV_CH;      // no request brings more rows than T - B + 1
-    const size_t per_row = (size_t)(2 * 3 * DKP + 2 * DVP + 2 + KG * DVP) * sizeof(float);
+    const size_t per_row = (size_t)(WKV_STAGES * 3 * DKP + WKV_STAGES * DVP + WKV_STAGES + KG * DVP) * sizeof(float);
     if (a.ch * per_row > 160 * 1024) a.ch = (int)(160 * 1024 / per_row);
     if (a.ch < 1) return SHARPI_BAD_ARGUMENT;
     const size_t smem = a.ch * per_row;
@@ -299,7 +320,7 @@ SHARPI_API int sharpi_wkv_recurrence(const float* r, const float* k, const float
         const uintptr_t ptrs = reinterpret_cast<uintptr_t>(r) | reinterpret_cast<uintptr_t>(k) |
                                reinterpret_cast<uintptr_t>(wraw) | reinterpret_cast<uintptr_t>(v);
         s.aligned = (d % 4 == 0 && (ptrs & 15) == 0) ? 1 : 0;
-        if (d % 4 == 0) return launch_wkv_scan<8, 4, 512>(s, B, T, stream);
+        if (d % 4 == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) return launch_wkv_scan<8, 4, 512>(s, B, T, stream);
         if (d <= 88) return launch_wkv_scan<8, 1, 1024>(s, B, T, stream);
         return launch_wkv_scan<16, 1, 1024>(s, B, T, stream);
     }
