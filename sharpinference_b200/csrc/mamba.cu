@@ -136,6 +136,7 @@ struct ScanArgs {
 
 constexpr int SCAN_NPT = 8;      // states a lane keeps
 constexpr int SCAN_CH = 16;      // rows a chunk at most
+constexpr int SCAN_STAGES = 3;   // chunks in shared memory: one being walked, two on their way
 
 __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
@@ -150,7 +151,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 
 // A block of W warps (four, or one when that is what it takes to give every SM a block) serves CPB = W * 32 / G
 // channels of one request.  The rows' inputs arrive in shared memory
-// by cp.async, two chunks of SCAN_CH rows in flight: per row the block's channels of dtraw, x and z and the row's B
+// by cp.async, two chunks of SCAN_CH rows on their way while a third is walked: per row the block's channels of dtraw, x and z and the row's B
 // and C.  What does not depend on the state (the softplus of the step sizes, the silu of the gate) was formed over
 // all rows at once by the kernels before this one.
 template <typename TO, int G>    // G lanes a channel (a power of two): N <= 8 G
@@ -189,13 +190,13 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(ScanArgs a) {
     for (int i = 0; i < SCAN_NPT; ++i)
         A[i] = n0 + i < N ? -expf(a.a_log[(size_t)c * N + n0 + i]) * 1.4426950408889634f : 0.0f;
     // states beyond N stay zero in both buffers' B and C
-    if (NP != N) for (int i = threadIdx.x; i < 2 * buf_floats; i += blockDim.x) {
+    if (NP != N) for (int i = threadIdx.x; i < SCAN_STAGES * buf_floats; i += blockDim.x) {
         const int within = i % buf_floats, row_part = within % (4 * CPB + 2 * NP);
         if (row_part >= 4 * CPB && (row_part - 4 * CPB) % NP >= N) sm[i] = 0.0f;
     }
     const int live_ch = min(CPB, a.C - c0);
     auto fetch = [&](int t0, int buf) {
-        const int rows = min(CH, end - t0);
+        const int rows = max(0, min(CH, end - t0));           // none: an empty group keeps the count of groups even
         float* base = sm + buf * buf_floats;
         const int stride = 4 * CPB + 2 * NP;
         if (a.vec_ch) {
@@ -238,12 +239,14 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(ScanArgs a) {
         }
         cp_async_commit();
     };
-    if (first < end) fetch(first, 0);
+    fetch(first, 0);
+    fetch(first + CH, 1);
     int buf = 0;
-    for (int t0 = first; t0 < end; t0 += CH, buf ^= 1) {
+    for (int t0 = first; t0 < end; t0 += CH, buf = (buf + 1) % SCAN_STAGES) {
         const int rows = min(CH, end - t0);
-        if (t0 + CH < end) { fetch(t0 + CH, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-        __syncthreads();
+        cp_async_wait<1>();       // all but the newest group: this chunk is here
+        __syncthreads();          // ... for everyone, and everyone has left the chunk before
+        fetch(t0 + 2 * CH, (buf + 2) % SCAN_STAGES);         // two chunks ahead, into the buffer of the chunk before
         const float* base = sm + buf * buf_floats;
         const float dsk = a.dskip[c];
 #pragma unroll 1
@@ -266,7 +269,6 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(ScanArgs a) {
             if (live && sub == 0)
                 ((TO*)a.out)[(size_t)(t0 + tt) * a.C + c] = from_float<TO>(fmaf(dsk, xv, acc) * row[3 * CPB + cl]);
         }
-        __syncthreads();
     }
     if (live) {
         if (vec) {
@@ -291,7 +293,7 @@ static int launch_scan(ScanArgs a, int B, int T, cudaStream_t stream) {
     const int cpb = warps * (32 / G);
     const dim3 grid((a.C + cpb - 1) / cpb, B);
     a.ch = T - B + 1 < SCAN_CH ? (T - B + 1 < 1 ? 1 : T - B + 1) : SCAN_CH;    // no request brings more rows than T - B + 1
-    const size_t smem = (size_t)2 * a.ch * (4 * cpb + 2 * G * SCAN_NPT) * sizeof(float);
+    const size_t smem = (size_t)SCAN_STAGES * a.ch * (4 * cpb + 2 * G * SCAN_NPT) * sizeof(float);
     const uintptr_t chp = reinterpret_cast<uintptr_t>(a.dtraw) | reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.z);
     a.vec_ch = (a.C % 4 == 0 && cpb % 4 == 0 && a.ld_z % 4 == 0 && (chp & 15) == 0) ? 1 : 0;
     a.vec_bc = (a.N % 4 == 0 && a.col_b % 4 == 0 && a.col_c % 4 == 0 && a.ld_bc % 4 == 0 &&
